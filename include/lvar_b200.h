@@ -1,0 +1,111 @@
+/*
+ * lvar_b200 - C ABI of the B200 (sm_100a) sparse-attention kernels.
+ *
+ * Every entry point is asynchronous on the CUDA stream it is given, allocates nothing unless its
+ * comment says otherwise, and returns LVAR_OK or a negative LVAR_ERR_* code; lvar_last_error()
+ * gives the message of the calling thread's last failure.  All tensor pointers are DEVICE pointers.
+ * Tensors are bf16 [B, H, L, D] views with a contiguous last dimension; strides are in ELEMENTS.
+ *
+ * Each declaration names the interface of the reference project (Weepingchestnut/Lvar, paths relative
+ * to its root) that it stands in for.
+ */
+#ifndef LVAR_B200_H_
+#define LVAR_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LVAR_OK 0
+#define LVAR_ERR_ARG (-1)          /* bad pointer, shape, stride or flag */
+#define LVAR_ERR_UNSUPPORTED (-2)  /* valid request outside what the kernels cover (e.g. head dim) */
+#define LVAR_ERR_CUDA (-3)         /* a CUDA runtime or driver call failed */
+#define LVAR_ERR_LIMIT (-4)        /* a size exceeds a documented maximum */
+
+/* Device status word values (int32 in device memory, set by a kernel; 0 = fine). */
+#define LVAR_DEV_OK 0
+#define LVAR_DEV_TIMEOUT_PRODUCER 1
+#define LVAR_DEV_TIMEOUT_MMA 2
+#define LVAR_DEV_TIMEOUT_SOFTMAX 3
+#define LVAR_DEV_TIMEOUT_DRAIN 4
+#define LVAR_DEV_BAD_INDEX 5
+#define LVAR_DEV_FORCED_TIMEOUT 6
+
+/* Default per-wait limit of the kernels' bounded waits, in nanoseconds. */
+#define LVAR_DEFAULT_WAIT_NS 2000000000ull
+
+typedef void* lvar_stream_t; /* a cudaStream_t */
+
+/* Argument block shared by the three attention entry points. Zero-initialise, then fill. */
+typedef struct lvar_attn_args {
+  /* problem */
+  int32_t B, H, Lq, Lkv, D; /* D in {64, 128}; query heads == kv heads */
+  float scale;              /* softmax scale (> 0), applied to q.k before the softmax */
+  /* q [B,H,Lq,D], k/v [B,H,Lkv,D], o [B,H,Lq,D]: bf16, 16-byte aligned, strides multiples of 8 */
+  const void* q;
+  int64_t q_sb, q_sh, q_sl;
+  const void* k;
+  int64_t k_sb, k_sh, k_sl;
+  const void* v;
+  int64_t v_sb, v_sh, v_sl;
+  void* o;
+  int64_t o_sb, o_sh, o_sl;
+  /* optional row statistics, fp32 [B,H,Lq] contiguous (dense / block-sparse only):
+   *   M = max_j(s_ij * scale) * log2(e),  L = sum_j exp2(s_ij * scale * log2e - M)  */
+  float* M;
+  float* L;
+  /* block-sparse only: uint8 mask [*, *, ceil(Lq/128), ceil(Lkv/128)], nonzero = attend.
+   * A stride of 0 broadcasts over batch / head. Innermost stride is 1. */
+  const uint8_t* block_mask;
+  int64_t bm_sb, bm_sh, bm_sq;
+  /* column-sparse only */
+  const int32_t* indices; /* [B,H,G,>=max count], G = ceil(Lq/group_rows); entries in [0,Lkv) */
+  int64_t i_sb, i_sh, i_sg;
+  const int32_t* counts; /* [B,H,G]: number of leading entries of each list that are used */
+  int64_t c_sb, c_sh;
+  int32_t group_rows; /* query rows that share one index list ("bm") */
+  const void* o_in;   /* bf16 [B,H,Lq,D] accumulate input; may be the same buffer as o */
+  int64_t oi_sb, oi_sh, oi_sl;
+  int32_t o_scale; /* +1 or -1 */
+  /* plumbing */
+  int32_t* dev_status;    /* optional device int32, must be zeroed by the caller; see LVAR_DEV_* */
+  uint64_t wait_limit_ns; /* per-wait limit of the kernel's bounded waits; 0 forces every pending wait to fail */
+  float* dbg;             /* optional device fp32 [128*128]: raw S of the first KV tile of CTA (0,0) */
+} lvar_attn_args;
+
+/* Dense attention o = softmax(q k^T * scale) v with row statistics.
+ * Replaces torch.ops.chipmunk.dense_attn (kernels/chipmunk/csrc/attn/dense_attn.cu:248-372) and
+ * sattn_triton.dense_attn (kernels/sparse_attn/triton/attn_dense.py:186-231), called from
+ * kernels/sparse_attn/sparse_attn_ops.py:21-59 and models/sparvar/basic_sparvar.py:384. */
+int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream);
+
+/* Block-sparse attention under a 128x128 block mask; rows whose blocks are all masked give 0.
+ * Replaces flex_attention(q, k, v, block_mask=...) in SparseFlexAttn.forward
+ * (models/sparvar/basic_sparvar.py:187-194). */
+int lvar_block_sparse_attn(const lvar_attn_args* args, lvar_stream_t stream);
+
+/* Column-sparse ("csp") attention: for each group of `group_rows` queries, attention over the keys
+ * listed in indices[b,h,g,:counts[b,h,g]] (a multiset), then o = o_in + o_scale * delta.
+ * Replaces torch.ops.chipmunk.csp_attn (kernels/chipmunk/csrc/attn/csp_attn.cu:318-433) and
+ * sattn_triton.csp_attn (kernels/sparse_attn/triton/attn_csp.py:215-265), called from
+ * kernels/sparse_attn/sparse_attn_ops.py:273-292. Unlike the reference, counts need not be a
+ * multiple of the KV tile. */
+int lvar_csp_attn(const lvar_attn_args* args, lvar_stream_t stream);
+
+/* Message of the calling thread's most recent failing call ("" if none). Never NULL. */
+const char* lvar_last_error(void);
+
+/* Library version, e.g. "0.1.0". */
+const char* lvar_version(void);
+
+/* Tile geometry callers must respect, the counterpart of get_kernel_config_attn()
+ * (kernels/sparse_attn/sparse_attn_config.py:82-98). */
+void lvar_kernel_config_attn(int32_t* bm, int32_t* counts_multiple_of, int32_t* indices_pad_to);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LVAR_B200_H_ */

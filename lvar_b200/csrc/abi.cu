@@ -1,0 +1,93 @@
+// extern "C" surface of the library (declared in include/lvar_b200.h) plus the host helpers the
+// launchers share.  No torch types cross this boundary.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace lvar {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda dependency.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+int encode_bhld_map(CUtensorMap* out, const void* base, int B, int H, int L, int D, int64_t sb, int64_t sh,
+                    int64_t sl, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  LVAR_REQUIRE(fn != nullptr, LVAR_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available (no CUDA driver?)");
+  // A stride of zero is not encodable; size-1 dimensions get a harmless dummy stride.
+  const cuuint64_t row_bytes = (cuuint64_t)D * 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t st_l = (cuuint64_t)sl * 2, st_h = (cuuint64_t)sh * 2, st_b = (cuuint64_t)sb * 2;
+  if (L == 1 && st_l == 0) st_l = row_bytes;
+  if (H == 1 && st_h == 0) st_h = st_l * (cuuint64_t)L;
+  if (B == 1 && st_b == 0) st_b = st_h * (cuuint64_t)H;
+  LVAR_REQUIRE(st_l >= row_bytes && st_h > 0 && st_b > 0, LVAR_ERR_ARG,
+               "tensor strides must be positive (got l=%lld h=%lld b=%lld elements)", (long long)sl, (long long)sh,
+               (long long)sb);
+  cuuint64_t strides[3] = {st_l, st_h, st_b};
+  cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1u, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LVAR_REQUIRE(r == CUDA_SUCCESS, LVAR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return LVAR_OK;
+}
+
+int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream);
+
+}  // namespace lvar
+
+extern "C" {
+
+int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream) {
+  return lvar::launch_attention(args, 0, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_block_sparse_attn(const lvar_attn_args* args, lvar_stream_t stream) {
+  return lvar::launch_attention(args, 1, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_csp_attn(const lvar_attn_args* args, lvar_stream_t stream) {
+  return lvar::launch_attention(args, 2, static_cast<cudaStream_t>(stream));
+}
+
+const char* lvar_last_error(void) { return lvar::g_err; }
+
+const char* lvar_version(void) { return "0.1.0"; }
+
+void lvar_kernel_config_attn(int32_t* bm, int32_t* counts_multiple_of, int32_t* indices_pad_to) {
+  if (bm) *bm = 256;
+  if (counts_multiple_of) *counts_multiple_of = 128;
+  if (indices_pad_to) *indices_pad_to = 4;
+}
+
+}  // extern "C"

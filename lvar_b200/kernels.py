@@ -1,0 +1,149 @@
+"""Torch-tensor front ends of the C ABI: pointer, stride and stream plumbing only.
+
+Each function validates what the C side cannot see (dtype, device), allocates outputs with torch,
+launches on the current CUDA stream and returns without synchronising.  Nothing here computes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import AttnArgs, check, lib
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda_bf16(name: str, t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (lvar_b200 has no CPU path)")
+    if t.dtype != torch.bfloat16:
+        raise RuntimeError(f"{name} must be bfloat16, got {t.dtype}")
+    if t.dim() != 4:
+        raise RuntimeError(f"{name} must be 4-dimensional [B, H, L, D], got {tuple(t.shape)}")
+    if t.stride(-1) != 1:
+        raise RuntimeError(f"{name} must have a contiguous last dimension")
+
+
+def _fill_qkv(a: AttnArgs, q, k, v, o, scale) -> None:
+    B, H, Lq, D = q.shape
+    if k.shape[0] != B or k.shape[1] != H or v.shape[:2] != k.shape[:2]:
+        raise RuntimeError(f"q/k/v batch or head mismatch (query heads must equal kv heads): "
+                           f"q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    if k.shape[-1] != D or v.shape[-1] != D or k.shape[2] != v.shape[2]:
+        raise RuntimeError(f"q/k/v shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    a.B, a.H, a.Lq, a.Lkv, a.D = B, H, Lq, k.shape[2], D
+    a.scale = float(D ** -0.5 if scale is None else scale)
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
+        setattr(a, name, t.data_ptr())
+        setattr(a, name + "_sb", t.stride(0))
+        setattr(a, name + "_sh", t.stride(1))
+        setattr(a, name + "_sl", t.stride(2))
+    a.wait_limit_ns = _lib.DEFAULT_WAIT_NS
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device status word for the kernels' bounded waits."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor) -> Tuple[int, str]:
+    """Synchronising read of a status word -> (code, description)."""
+    code = int(status.item())
+    return code, _lib.DEV_STATUS_NAMES.get(code, f"unknown status {code}")
+
+
+def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None, dbg=None):
+    """o = softmax(q k^T * scale) v; returns (o, M, L) with fp32 [B,H,Lq] statistics in base 2."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(n, t)
+    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    B, H, Lq, _ = q.shape
+    M = L = None
+    a = AttnArgs()
+    _fill_qkv(a, q, k, v, o, scale)
+    if return_stats:
+        M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        L = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        a.M, a.L = M.data_ptr(), L.data_ptr()
+    if status is not None:
+        a.dev_status = status.data_ptr()
+    if wait_limit_ns is not None:
+        a.wait_limit_ns = int(wait_limit_ns)
+    if dbg is not None:
+        a.dbg = dbg.data_ptr()
+    check(lib.lvar_dense_attn(C.byref(a), _stream_ptr(q.device)))
+    return o, M, L
+
+
+def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None):
+    """Attention under a 128x128 block mask (uint8/bool, shape [nq,nk], [H,nq,nk] or [B,H,nq,nk])."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(n, t)
+    B, H, Lq, _ = q.shape
+    Lkv = k.shape[2]
+    nq, nk = (Lq + 127) // 128, (Lkv + 127) // 128
+    m = block_mask
+    if m.dtype == torch.bool:
+        m = m.view(torch.uint8)
+    if m.dtype != torch.uint8 or not m.is_cuda:
+        raise RuntimeError("block_mask must be a CUDA bool or uint8 tensor")
+    while m.dim() < 4:
+        m = m.unsqueeze(0)
+    if m.shape[-2:] != (nq, nk) or m.shape[0] not in (1, B) or m.shape[1] not in (1, H):
+        raise RuntimeError(f"block_mask shape {tuple(block_mask.shape)} does not match "
+                           f"[{B}|1, {H}|1, {nq}, {nk}]")
+    if m.stride(-1) != 1:
+        m = m.contiguous()
+    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    a = AttnArgs()
+    _fill_qkv(a, q, k, v, o, scale)
+    a.block_mask = m.data_ptr()
+    a.bm_sb = m.stride(0) if m.shape[0] > 1 else 0
+    a.bm_sh = m.stride(1) if m.shape[1] > 1 else 0
+    a.bm_sq = m.stride(2)
+    M = L = None
+    if return_stats:
+        M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        L = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        a.M, a.L = M.data_ptr(), L.data_ptr()
+    if status is not None:
+        a.dev_status = status.data_ptr()
+    check(lib.lvar_block_sparse_attn(C.byref(a), _stream_ptr(q.device)))
+    return (o, M, L) if return_stats else o
+
+
+def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None, *, out=None, status=None):
+    """out = o_in + o_scale * softmax(q k[idx]^T * scale) v[idx] per query group of `group_rows` rows."""
+    for n, t in (("q", q), ("k", k), ("v", v), ("o", o_in)):
+        _require_cuda_bf16(n, t)
+    B, H, Lq, _ = q.shape
+    G = (Lq + group_rows - 1) // group_rows
+    if indices.dtype != torch.int32 or counts.dtype != torch.int32 or not indices.is_cuda or not counts.is_cuda:
+        raise RuntimeError("indices and counts must be CUDA int32 tensors")
+    if tuple(indices.shape[:3]) != (B, H, G) or tuple(counts.shape) != (B, H, G):
+        raise RuntimeError(f"indices {tuple(indices.shape)} / counts {tuple(counts.shape)} do not match "
+                           f"[B={B}, H={H}, G={G}, *]")
+    if indices.stride(-1) != 1 or counts.stride(-1) != 1:
+        raise RuntimeError("indices and counts must have a contiguous last dimension")
+    if o_in.shape != q.shape:
+        raise RuntimeError("Output shape mismatch - o: {}, q: {}".format(tuple(o_in.shape), tuple(q.shape)))
+    o = torch.empty_like(q, memory_format=torch.contiguous_format) if out is None else out
+    a = AttnArgs()
+    _fill_qkv(a, q, k, v, o, scale)
+    a.indices = indices.data_ptr()
+    a.i_sb, a.i_sh, a.i_sg = indices.stride(0), indices.stride(1), indices.stride(2)
+    a.counts = counts.data_ptr()
+    a.c_sb, a.c_sh = counts.stride(0), counts.stride(1)
+    a.group_rows = int(group_rows)
+    a.o_in = o_in.data_ptr()
+    a.oi_sb, a.oi_sh, a.oi_sl = o_in.stride(0), o_in.stride(1), o_in.stride(2)
+    a.o_scale = int(o_scale)
+    if status is not None:
+        a.dev_status = status.data_ptr()
+    check(lib.lvar_csp_attn(C.byref(a), _stream_ptr(q.device)))
+    return o
