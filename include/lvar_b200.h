@@ -94,6 +94,21 @@ int lvar_block_sparse_attn(const lvar_attn_args* args, lvar_stream_t stream);
  * multiple of the KV tile. */
 int lvar_csp_attn(const lvar_attn_args* args, lvar_stream_t stream);
 
+/* Attention column sums (KV-importance scores) given the row statistics of a previous attention pass:
+ *   cs[b,h,g,j] = sum_{i in group g} exp2(q_i.k_j * scale * log2e - M_i) / L_i,   g = i / group_rows
+ * q [B,H,Lq,D], k [B,H,Lkv,D] bf16; M, L fp32 [B,H,Lq] contiguous (as written by lvar_dense_attn);
+ * cs fp32 [B,H,ceil(Lq/group_rows),Lkv] with the given strides (innermost 1); every element is
+ * written, no zero-fill needed, and the summation order is fixed (bit-reproducible).
+ * group_rows must be a multiple of 32.
+ * Replaces the second sweep of _full_attn_fwd (kernels/sparse_attn/triton/attn_dense_colsum.py:198-234)
+ * and the colsum of torch.ops.chipmunk.dense_colsum_attn(q,k,v,p)
+ * (kernels/chipmunk/csrc/attn/dense_colsum_attn.cu:354-522), reached through dense_colsum_attn_q/_s
+ * (kernels/sparse_attn/sparse_attn_ops.py:65-149). */
+int lvar_colsum(const void* q, const void* k, const float* M, const float* L, float* cs, int32_t B, int32_t H,
+                int32_t Lq, int32_t Lkv, int32_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb,
+                int64_t k_sh, int64_t k_sl, int64_t cs_sb, int64_t cs_sh, int64_t cs_sg, int32_t group_rows,
+                float scale, int32_t* dev_status, uint64_t wait_limit_ns, lvar_stream_t stream);
+
 /* Message of the calling thread's most recent failing call ("" if none). Never NULL. */
 const char* lvar_last_error(void);
 

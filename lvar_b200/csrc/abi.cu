@@ -63,6 +63,10 @@ int encode_bhld_map(CUtensorMap* out, const void* base, int B, int H, int L, int
 }
 
 int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream);
+int launch_colsum(const void* q, const void* k, const float* M, const float* L, float* cs, int B, int H, int Lq,
+                  int Lkv, int D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                  int64_t cs_sb, int64_t cs_sh, int64_t cs_sg, int group_rows, float scale, int* dev_status,
+                  uint64_t wait_limit_ns, cudaStream_t stream);
 
 }  // namespace lvar
 
@@ -78,6 +82,14 @@ int lvar_block_sparse_attn(const lvar_attn_args* args, lvar_stream_t stream) {
 
 int lvar_csp_attn(const lvar_attn_args* args, lvar_stream_t stream) {
   return lvar::launch_attention(args, 2, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_colsum(const void* q, const void* k, const float* M, const float* L, float* cs, int32_t B, int32_t H,
+                int32_t Lq, int32_t Lkv, int32_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb,
+                int64_t k_sh, int64_t k_sl, int64_t cs_sb, int64_t cs_sh, int64_t cs_sg, int32_t group_rows,
+                float scale, int32_t* dev_status, uint64_t wait_limit_ns, lvar_stream_t stream) {
+  return lvar::launch_colsum(q, k, M, L, cs, B, H, Lq, Lkv, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, cs_sb, cs_sh,
+                             cs_sg, group_rows, scale, dev_status, wait_limit_ns, static_cast<cudaStream_t>(stream));
 }
 
 const char* lvar_last_error(void) { return lvar::g_err; }

@@ -147,3 +147,25 @@ def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None
         a.dev_status = status.data_ptr()
     check(lib.lvar_csp_attn(C.byref(a), _stream_ptr(q.device)))
     return o
+
+
+def colsum_fwd(q, k, M, L, group_rows, scale=None, *, status=None):
+    """cs[b,h,g,j] = sum over the rows of query group g of softmax(q k^T * scale)[., j]; fp32 out."""
+    _require_cuda_bf16("q", q)
+    _require_cuda_bf16("k", k)
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    if k.shape[0] != B or k.shape[1] != H or k.shape[3] != D:
+        raise RuntimeError(f"q/k shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}")
+    for n, t in (("M", M), ("L", L)):
+        if t.dtype != torch.float32 or not t.is_cuda or t.numel() != B * H * Lq or not t.is_contiguous():
+            raise RuntimeError(f"{n} must be a contiguous CUDA float32 tensor with B*H*Lq elements")
+    G = (Lq + group_rows - 1) // group_rows
+    cs = torch.empty((B, H, G, Lkv), dtype=torch.float32, device=q.device)
+    sc = float(D ** -0.5 if scale is None else scale)
+    check(lib.lvar_colsum(q.data_ptr(), k.data_ptr(), M.data_ptr(), L.data_ptr(), cs.data_ptr(),
+                          B, H, Lq, Lkv, D, q.stride(0), q.stride(1), q.stride(2),
+                          k.stride(0), k.stride(1), k.stride(2), cs.stride(0), cs.stride(1), cs.stride(2),
+                          int(group_rows), sc, status.data_ptr() if status is not None else None,
+                          _lib.DEFAULT_WAIT_NS, _stream_ptr(q.device)))
+    return cs
