@@ -109,6 +109,47 @@ int lvar_colsum(const void* q, const void* k, const float* M, const float* L, fl
                 int64_t k_sh, int64_t k_sl, int64_t cs_sb, int64_t cs_sh, int64_t cs_sg, int32_t group_rows,
                 float scale, int32_t* dev_status, uint64_t wait_limit_ns, lvar_stream_t stream);
 
+/* Per-KV-block scores: out[r, j] = sum of cs[r, j*block : (j+1)*block] (columns past Lkv count as 0),
+ * r over `rows` = B*H*G rows of cs spaced cs_row_stride elements apart; out is [rows, ceil(Lkv/block)]
+ * contiguous.  Fixed summation order.  Feeds the block top-k that the benchmark's mask recipe and a
+ * block-level version of the decision step (models/sparvar/sparse_attn.py:1012-1016) need. */
+int lvar_block_scores(const float* cs, float* out, int64_t rows, int32_t Lkv, int32_t block,
+                      int64_t cs_row_stride, lvar_stream_t stream);
+
+/* Block mask = always-kept blocks U the highest-scoring remaining blocks, so that every row has
+ * max(k_total, |always|) active blocks.  scores fp32 [BH, nq, nk]; always uint8 [nq, nk] or NULL;
+ * mask uint8 [BH, nq, nk] out; optional lists int32 [BH, nq, nk] (active block ids ascending, tail -1)
+ * and counts int32 [BH, nq].  Descending score, lower block index wins a tie.
+ * The block-level counterpart of the reference's sink + local-window + top-k policy
+ * (models/sparvar/basic_sparvar.py:109-173, models/sparvar/sparse_attn.py:1012-1036). */
+int lvar_build_block_mask(const float* scores, const uint8_t* always, uint8_t* mask, int32_t* lists,
+                          int32_t* counts, int64_t BH, int32_t nq, int32_t nk, int32_t k_total,
+                          lvar_stream_t stream);
+
+/* Exact, deterministic top-k of each row of an fp32 matrix [rows, n] (row_stride elements apart).
+ * out int32 [rows, out_cols] (out_stride apart): the first k entries are the selected column ids,
+ * descending by value with equal values in ascending index order, or, if ascending_index != 0, the
+ * same set sorted by index; entries k..out_cols-1 are set to 0.  counts (optional, int32 [rows]) is
+ * set to count_value.  Shared memory bounds the row: 4*n + 8*nextpow2(k) <= 204800 bytes.
+ * Replaces torch.topk(bs, k, dim=-1).indices + the padding that follows it
+ * (models/sparvar/sparse_attn.py:1016-1036) and the approximate torch.ops.chipmunk.topk_indices
+ * (kernels/chipmunk/csrc/indexed_io/topk_indices.cu:145-218). */
+int lvar_topk_indices(const float* scores, int64_t rows, int32_t n, int64_t row_stride, int32_t k,
+                      int32_t ascending_index, int32_t* out, int64_t out_stride, int32_t out_cols,
+                      int32_t* counts, int32_t count_value, lvar_stream_t stream);
+
+/* bool/uint8 mask [rows, n] -> index lists int32 [rows, pad_n] and counts int32 [rows]; same list
+ * order and padding rule as torch.ops.chipmunk.mask_to_indices
+ * (kernels/chipmunk/csrc/indexed_io/mask_to_indices.cu:21-142): grouped by (column mod 32), count
+ * rounded up to multiple_of with the first unset columns.  Entries past the count are not written. */
+int lvar_mask_to_indices(const uint8_t* mask, int32_t* indices, int32_t* counts, int64_t rows, int32_t n,
+                         int32_t pad_n, int32_t multiple_of, lvar_stream_t stream);
+
+/* Little-endian bit packing of n_bits bool bytes into ceil(n_bits/8) bytes, and its inverse
+ * (kernels/sparse_attn/sparse_attn_ops.py:300-366). */
+int lvar_bitpack(const uint8_t* mask, uint8_t* packed, int64_t n_bits, lvar_stream_t stream);
+int lvar_bitunpack(const uint8_t* packed, uint8_t* mask, int64_t n_bits, lvar_stream_t stream);
+
 /* Message of the calling thread's most recent failing call ("" if none). Never NULL. */
 const char* lvar_last_error(void);
 

@@ -68,6 +68,18 @@ int launch_colsum(const void* q, const void* k, const float* M, const float* L, 
                   int64_t cs_sb, int64_t cs_sh, int64_t cs_sg, int group_rows, float scale, int* dev_status,
                   uint64_t wait_limit_ns, cudaStream_t stream);
 
+int launch_block_scores(const float* cs, float* out, int64_t rows, int Lkv, int block, int64_t cs_row_stride,
+                        cudaStream_t stream);
+int launch_build_block_mask(const float* scores, const uint8_t* always, uint8_t* mask, int32_t* lists,
+                            int32_t* counts, int64_t BH, int nq, int nk, int k_total, cudaStream_t stream);
+int launch_topk(const float* scores, int64_t rows, int n, int64_t row_stride, int k, int ascending_index,
+                int32_t* out, int64_t out_stride, int out_cols, int32_t* counts, int count_value,
+                cudaStream_t stream);
+int launch_mask_to_indices(const uint8_t* mask, int32_t* indices, int32_t* counts, int64_t rows, int n, int pad_n,
+                           int multiple_of, cudaStream_t stream);
+int launch_bitpack(const uint8_t* mask, uint8_t* packed, int64_t n_bits, cudaStream_t stream);
+int launch_bitunpack(const uint8_t* packed, uint8_t* mask, int64_t n_bits, cudaStream_t stream);
+
 }  // namespace lvar
 
 extern "C" {
@@ -90,6 +102,39 @@ int lvar_colsum(const void* q, const void* k, const float* M, const float* L, fl
                 float scale, int32_t* dev_status, uint64_t wait_limit_ns, lvar_stream_t stream) {
   return lvar::launch_colsum(q, k, M, L, cs, B, H, Lq, Lkv, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, cs_sb, cs_sh,
                              cs_sg, group_rows, scale, dev_status, wait_limit_ns, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_block_scores(const float* cs, float* out, int64_t rows, int32_t Lkv, int32_t block,
+                      int64_t cs_row_stride, lvar_stream_t stream) {
+  return lvar::launch_block_scores(cs, out, rows, Lkv, block, cs_row_stride, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_build_block_mask(const float* scores, const uint8_t* always, uint8_t* mask, int32_t* lists,
+                          int32_t* counts, int64_t BH, int32_t nq, int32_t nk, int32_t k_total,
+                          lvar_stream_t stream) {
+  return lvar::launch_build_block_mask(scores, always, mask, lists, counts, BH, nq, nk, k_total,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+int lvar_topk_indices(const float* scores, int64_t rows, int32_t n, int64_t row_stride, int32_t k,
+                      int32_t ascending_index, int32_t* out, int64_t out_stride, int32_t out_cols,
+                      int32_t* counts, int32_t count_value, lvar_stream_t stream) {
+  return lvar::launch_topk(scores, rows, n, row_stride, k, ascending_index, out, out_stride, out_cols, counts,
+                           count_value, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_mask_to_indices(const uint8_t* mask, int32_t* indices, int32_t* counts, int64_t rows, int32_t n,
+                         int32_t pad_n, int32_t multiple_of, lvar_stream_t stream) {
+  return lvar::launch_mask_to_indices(mask, indices, counts, rows, n, pad_n, multiple_of,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int lvar_bitpack(const uint8_t* mask, uint8_t* packed, int64_t n_bits, lvar_stream_t stream) {
+  return lvar::launch_bitpack(mask, packed, n_bits, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_bitunpack(const uint8_t* packed, uint8_t* mask, int64_t n_bits, lvar_stream_t stream) {
+  return lvar::launch_bitunpack(packed, mask, n_bits, static_cast<cudaStream_t>(stream));
 }
 
 const char* lvar_last_error(void) { return lvar::g_err; }

@@ -169,3 +169,103 @@ def colsum_fwd(q, k, M, L, group_rows, scale=None, *, status=None):
                           int(group_rows), sc, status.data_ptr() if status is not None else None,
                           _lib.DEFAULT_WAIT_NS, _stream_ptr(q.device)))
     return cs
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def block_scores(cs: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """[B,H,G,Lkv] fp32 column sums -> [B,H,G,ceil(Lkv/block)] fp32 per-KV-block sums."""
+    _require(cs.is_cuda and cs.dtype == torch.float32 and cs.dim() == 4 and cs.stride(-1) == 1,
+             "cs must be a CUDA float32 [B,H,G,Lkv] tensor with a contiguous last dimension")
+    if not cs.is_contiguous():
+        cs = cs.contiguous()
+    B, H, G, Lkv = cs.shape
+    nk = (Lkv + block - 1) // block
+    out = torch.empty((B, H, G, nk), dtype=torch.float32, device=cs.device)
+    check(lib.lvar_block_scores(cs.data_ptr(), out.data_ptr(), B * H * G, Lkv, int(block), cs.stride(2),
+                                _stream_ptr(cs.device)))
+    return out
+
+
+def build_block_mask(scores: torch.Tensor, always: Optional[torch.Tensor], k_total: int, *, return_lists=False):
+    """scores fp32 [B,H,nq,nk], always bool/uint8 [nq,nk] or None -> bool mask [B,H,nq,nk]
+    (and, with return_lists, int32 lists [B,H,nq,nk] padded with -1 and counts [B,H,nq])."""
+    _require(scores.is_cuda and scores.dtype == torch.float32 and scores.dim() == 4,
+             "scores must be a CUDA float32 [B,H,nq,nk] tensor")
+    scores = scores.contiguous()
+    B, H, nq, nk = scores.shape
+    a_ptr = None
+    if always is not None:
+        _require(always.is_cuda and tuple(always.shape) == (nq, nk), f"always must be a CUDA [{nq},{nk}] tensor")
+        always = always.to(torch.uint8).contiguous() if always.dtype != torch.uint8 else always.contiguous()
+        a_ptr = always.data_ptr()
+    mask = torch.empty((B, H, nq, nk), dtype=torch.uint8, device=scores.device)
+    lists = counts = None
+    if return_lists:
+        lists = torch.empty((B, H, nq, nk), dtype=torch.int32, device=scores.device)
+        counts = torch.empty((B, H, nq), dtype=torch.int32, device=scores.device)
+    check(lib.lvar_build_block_mask(scores.data_ptr(), a_ptr, mask.data_ptr(),
+                                    lists.data_ptr() if lists is not None else None,
+                                    counts.data_ptr() if counts is not None else None,
+                                    B * H, nq, nk, int(k_total), _stream_ptr(scores.device)))
+    mask = mask.view(torch.bool)
+    return (mask, lists, counts) if return_lists else mask
+
+
+def topk_indices(scores: torch.Tensor, k: int, *, ascending_index=False, out_cols: Optional[int] = None,
+                 with_counts=False):
+    """Exact deterministic top-k along the last dim of a float32 tensor -> int32 [..., out_cols]
+    (first k entries valid, the rest 0) and optionally counts [...] filled with k."""
+    _require(scores.is_cuda and scores.dtype == torch.float32 and scores.stride(-1) == 1,
+             "scores must be a CUDA float32 tensor with a contiguous last dimension")
+    n = scores.shape[-1]
+    lead = scores.shape[:-1]
+    flat = scores.reshape(-1, n)
+    rows = flat.shape[0]
+    cols = int(k if out_cols is None else out_cols)
+    out = torch.empty((rows, cols), dtype=torch.int32, device=scores.device)
+    counts = torch.empty((rows,), dtype=torch.int32, device=scores.device) if with_counts else None
+    check(lib.lvar_topk_indices(flat.data_ptr(), rows, n, flat.stride(0), int(k), int(bool(ascending_index)),
+                                out.data_ptr(), out.stride(0), cols,
+                                counts.data_ptr() if counts is not None else None, int(k),
+                                _stream_ptr(scores.device)))
+    out = out.view(*lead, cols)
+    return (out, counts.view(*lead)) if with_counts else out
+
+
+def mask_to_indices(mask: torch.Tensor, multiple_of: int, pad_to_multiple_of: int):
+    """bool [b,h,m,n] -> [indices int32 [b,h,m,n rounded up to pad_to], counts int32 [b,h,m]]."""
+    _require(mask.dim() == 4, "mask must be 4-dimensional [b, h, m, n]")
+    _require(mask.dtype == torch.bool, "mask must be bool type")
+    _require(mask.is_cuda, "mask must be a CUDA tensor (lvar_b200 has no CPU path)")
+    mask = mask.contiguous()
+    b, h, m, n = mask.shape
+    pad_n = (n + pad_to_multiple_of - 1) // pad_to_multiple_of * pad_to_multiple_of
+    indices = torch.empty((b, h, m, pad_n), dtype=torch.int32, device=mask.device)
+    counts = torch.empty((b, h, m), dtype=torch.int32, device=mask.device)
+    check(lib.lvar_mask_to_indices(mask.view(torch.uint8).data_ptr(), indices.data_ptr(), counts.data_ptr(),
+                                   b * h * m, n, pad_n, int(multiple_of), _stream_ptr(mask.device)))
+    return [indices, counts]
+
+
+def bitpack(mask: torch.Tensor):
+    _require(mask.is_cuda and mask.dtype == torch.bool, "mask must be a CUDA bool tensor")
+    flat = mask.contiguous().view(torch.uint8)
+    n = flat.numel()
+    packed = torch.empty(((n + 7) // 8,), dtype=torch.uint8, device=mask.device)
+    check(lib.lvar_bitpack(flat.data_ptr(), packed.data_ptr(), n, _stream_ptr(mask.device)))
+    return packed, mask.shape
+
+
+def bitunpack(packed: torch.Tensor, original_shape):
+    _require(packed.is_cuda and packed.dtype == torch.uint8 and packed.dim() == 1, "packed must be CUDA uint8 1-D")
+    total = 1
+    for d in original_shape:
+        total *= int(d)
+    _require(packed.numel() * 8 >= total, "packed tensor too short for the requested shape")
+    out = torch.empty((total,), dtype=torch.uint8, device=packed.device)
+    check(lib.lvar_bitunpack(packed.contiguous().data_ptr(), out.data_ptr(), total, _stream_ptr(packed.device)))
+    return out.view(torch.bool).view(*original_shape)
