@@ -87,6 +87,7 @@ struct Bars {
   uint64_t k_full[kStages], k_empty[kStages];
   uint64_t v_full[kStages], v_empty[kStages];
   uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t mma_done;
   uint32_t tmem_base;
   int abort_flag;
   int n_steps;
@@ -179,6 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&bars->p_full[s], 128);
       mbar_init(&bars->o_full[s], 1);
     }
+    mbar_init(&bars->mma_done, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -224,6 +226,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       a0 = slot_live[0] ? n : 0;
       a1 = slot_live[1] ? n : 0;
     }
+    if (!slot_live[0] && !slot_live[1]) n = 0;  // chunk past the end of its query group: nothing to do
     if (lane == 0) {
       bars->n_steps = (MODE == MODE_BLOCK) ? min(n, kMaxSteps) : n;
       bars->n_act[0] = a0;
@@ -580,6 +583,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) {
         if (npv[0] > 0) umma_commit(&bars->o_full[0]);
         if (npv[1] > 0) umma_commit(&bars->o_full[1]);
+      }
+      // TMEM must not be freed (nor the CTA retire) while an MMA is still in flight, also on abort.
+      umma_commit(&bars->mma_done);
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > 2000000000ull) {
+          if (p.status) atomicCAS(p.status, 0, (int)DEV_TIMEOUT_DRAIN);
+          break;
+        }
       }
     }
     __syncwarp();

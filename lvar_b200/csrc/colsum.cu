@@ -57,6 +57,7 @@ struct CsBars {
   uint64_t q_full[kQStages], q_empty[kQStages];
   uint64_t s_full[kSBufs], s_empty[kSBufs];
   uint64_t part_full[2], part_empty[2];
+  uint64_t mma_done;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -99,6 +100,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       mbar_init(&bars->part_full[i], 128);
       mbar_init(&bars->part_empty[i], 128);
     }
+    mbar_init(&bars->mma_done, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -268,6 +270,15 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         umma_commit(&bars->s_full[buf]);
         umma_commit(&bars->q_empty[st]);
+      }
+      // TMEM must not be freed while an MMA is still in flight, also on abort.
+      umma_commit(&bars->mma_done);
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > 2000000000ull) {
+          if (p.status) atomicCAS(p.status, 0, (int)DEV_TIMEOUT_DRAIN);
+          break;
+        }
       }
     }
     __syncwarp();

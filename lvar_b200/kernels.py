@@ -227,11 +227,13 @@ def topk_indices(scores: torch.Tensor, k: int, *, ascending_index=False, out_col
     rows = flat.shape[0]
     cols = int(k if out_cols is None else out_cols)
     out = torch.empty((rows, cols), dtype=torch.int32, device=scores.device)
-    counts = torch.empty((rows,), dtype=torch.int32, device=scores.device) if with_counts else None
-    check(lib.lvar_topk_indices(flat.data_ptr(), rows, n, flat.stride(0), int(k), int(bool(ascending_index)),
-                                out.data_ptr(), out.stride(0), cols,
-                                counts.data_ptr() if counts is not None else None, int(k),
-                                _stream_ptr(scores.device)))
+    counts = torch.full((rows,), int(k), dtype=torch.int32, device=scores.device) if with_counts else None
+    if cols > 0:
+        check(lib.lvar_topk_indices(flat.data_ptr(), rows, n, flat.stride(0), int(k),
+                                    int(bool(ascending_index)),
+                                    out.data_ptr(), out.stride(0), cols,
+                                    counts.data_ptr() if counts is not None else None, int(k),
+                                    _stream_ptr(scores.device)))
     out = out.view(*lead, cols)
     return (out, counts.view(*lead)) if with_counts else out
 

@@ -1,0 +1,268 @@
+"""GPU parity of the attention and column-sum kernels against the CPU oracle and the reference's golden
+outputs, through the C ABI (lvar_b200.kernels / lvar_b200.sparse_attn_ops).
+
+Tolerances (bf16 kernels against an fp32 oracle): outputs max-abs <= 2e-2 and mean-abs <= 2e-3;
+column sums <= 1e-3 relative; row statistics 1e-4 relative.
+"""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+O_MAX, O_MEAN, CS_REL = 2e-2, 2e-3, 1e-3
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lvar_b200 import kernels
+    return kernels
+
+
+def _qkv(B, H, Lq, Lkv, D, seed=0, peaked=False):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, Lq, D, generator=g)
+    k = torch.randn(B, H, Lkv, D, generator=g)
+    v = torch.randn(B, H, Lkv, D, generator=g)
+    if peaked:  # seeded rank-8 component on K so that the column sums are peaked
+        k = k + 2.0 * (torch.randn(B, H, Lkv, 8, generator=g) @ torch.randn(B, H, 8, D, generator=g))
+    return q.bfloat16(), k.bfloat16(), v.bfloat16()
+
+
+def _check_o(o_gpu, o_ref):
+    d = (o_gpu.float().cpu() - o_ref.float()).abs()
+    assert torch.isfinite(o_gpu.float()).all()
+    assert d.max().item() <= O_MAX, f"max-abs {d.max().item():.3e}"
+    assert d.mean().item() <= O_MEAN, f"mean-abs {d.mean().item():.3e}"
+
+
+def _ok_status(K, st):
+    code, text = K.read_status(st)
+    assert code == 0, text
+
+
+DENSE_SHAPES = [
+    (1, 1, 1, 1, 128), (1, 2, 5, 7, 64), (1, 2, 129, 257, 128), (2, 3, 300, 1000, 128), (2, 3, 300, 1000, 64),
+    (2, 16, 256, 680, 64),  # VAR-d16 last scale against all 10 scales
+    (1, 2, 1600, 4121, 128),  # Infinity decision scale
+]
+
+
+@pytest.mark.parametrize("B,H,Lq,Lkv,D", DENSE_SHAPES)
+def test_dense_attn_matches_oracle(K, B, H, Lq, Lkv, D):
+    from oracle import attention as oa
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq + Lkv)
+    st = K.new_status("cuda")
+    o, M, L = K.dense_attn_fwd(q.cuda(), k.cuda(), v.cuda(), None, status=st)
+    _ok_status(K, st)
+    o_ref, M_ref, L_ref = oa.dense_attn(q, k, v)
+    _check_o(o, o_ref)
+    assert torch.allclose(M.cpu(), M_ref, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(L.cpu(), L_ref, atol=0, rtol=1e-4)
+
+
+def test_dense_attn_scale_one_cosine_like(K):
+    """Cosine attention: unit-norm q and k scaled by a per-head factor, softmax scale 1."""
+    from oracle import attention as oa
+    q, k, v = _qkv(1, 4, 520, 1100, 128, seed=3)
+    q = (torch.nn.functional.normalize(q.float(), dim=-1) * 8.0).bfloat16()
+    k = torch.nn.functional.normalize(k.float(), dim=-1).bfloat16()
+    o, M, L = K.dense_attn_fwd(q.cuda(), k.cuda(), v.cuda(), 1.0)
+    o_ref, _, _ = oa.dense_attn(q, k, v, 1.0)
+    _check_o(o, o_ref)
+
+
+def test_dense_attn_strided_views(K):
+    """q/k/v as slices of one packed [B, L, 3, H, D] projection (no copies needed)."""
+    from oracle import attention as oa
+    g = torch.Generator().manual_seed(5)
+    packed = torch.randn(2, 384, 3, 4, 64, generator=g).bfloat16()
+    q, k, v = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    pc = packed.cuda()
+    qc, kc, vc = (pc[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    o, _, _ = K.dense_attn_fwd(qc, kc, vc)
+    _check_o(o, oa.dense_attn(q, k, v)[0])
+
+
+def test_golden_colsum_cases(K, golden_attention):
+    """The reference's naive_dense_colsum_attn / reference_blocksums outputs on stored inputs."""
+    g = golden_attention
+    for tag in ("a", "b"):
+        q, k, v = (g[f"colsum_{tag}_{n}"].bfloat16().cuda() for n in "qkv")
+        bm = int(g[f"colsum_{tag}_bm"])
+        o, M, L = K.dense_attn_fwd(q, k, v)
+        cs = K.colsum_fwd(q, k, M, L, bm)
+        _check_o(o, g[f"colsum_{tag}_o"])
+        ref = g[f"colsum_{tag}_cs"]
+        rel = ((cs.cpu() - ref).abs() / ref.abs().clamp_min(1e-30)).max().item()
+        assert rel <= CS_REL, f"colsum relative error {rel:.3e}"
+
+
+@pytest.mark.parametrize("B,H,Lq,Lkv,D,bm", [
+    (1, 1, 1, 1, 64, 256), (1, 2, 31, 5, 128, 32), (2, 3, 300, 1000, 128, 192), (2, 3, 700, 1300, 64, 256),
+    (2, 16, 256, 680, 64, 64), (1, 2, 1600, 4121, 128, 192), (1, 2, 1600, 4121, 128, 256)])
+def test_colsum_matches_oracle(K, B, H, Lq, Lkv, D, bm):
+    from oracle import attention as oa
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=bm + Lq, peaked=True)
+    st = K.new_status("cuda")
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o, M, L = K.dense_attn_fwd(qc, kc, vc, status=st)
+    cs = K.colsum_fwd(qc, kc, M, L, bm, status=st)
+    _ok_status(K, st)
+    _, cs_ref = oa.dense_colsum_attn(q, k, v, None, q_group_size=bm, dtype=torch.float64)
+    rel = ((cs.double().cpu() - cs_ref).abs() / cs_ref.abs().clamp_min(1e-300)).max().item()
+    assert rel <= CS_REL, f"colsum relative error {rel:.3e}"
+    assert torch.equal(cs, K.colsum_fwd(qc, kc, M, L, bm)), "colsum must be bit-reproducible"
+
+
+def test_block_sparse_matches_oracle(K):
+    from oracle import attention as oa
+    for (B, H, Lq, Lkv, D, dens, seed) in [(2, 2, 700, 1500, 128, 0.4, 1), (1, 3, 130, 400, 64, 0.5, 2),
+                                          (1, 2, 1024, 1024, 128, 0.15, 3)]:
+        q, k, v = _qkv(B, H, Lq, Lkv, D, seed=seed)
+        nq, nk = (Lq + 127) // 128, (Lkv + 127) // 128
+        g = torch.Generator().manual_seed(seed)
+        bm = torch.rand(B, H, nq, nk, generator=g) < dens
+        bm[..., 0] = True
+        bm[0, 0, -1] = False  # one fully masked row of blocks -> zeros
+        st = K.new_status("cuda")
+        o = K.block_sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), bm.cuda(), status=st)
+        _ok_status(K, st)
+        _check_o(o, oa.block_sparse_attn(q, k, v, bm))
+        assert o[0, 0, (nq - 1) * 128:].abs().max().item() == 0.0
+    # broadcast mask [nq, nk]
+    q, k, v = _qkv(2, 2, 300, 500, 128, seed=9)
+    bm = torch.tensor([[1, 0, 1, 1], [0, 1, 0, 1], [1, 1, 1, 0]], dtype=torch.bool)
+    o = K.block_sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), bm.cuda())
+    _check_o(o, oa.block_sparse_attn(q, k, v, bm))
+
+
+def test_block_sparse_csla_mask_last_scale(K):
+    """Static sink + local-window block mask of the last Infinity scale (Lq 4096, Lkv 10521), one head."""
+    from lvar_b200 import policy as P
+    from oracle import attention as oa
+    scales = P.INFINITY_SCALES
+    mask = P.csla_block_mask([(s, s) for s in scales], [-1] * 8 + [1, 1, 3, 5, 7], 12, 5)
+    q, k, v = _qkv(1, 1, 4096, 10521, 128, seed=12)
+    o = K.block_sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), mask.cuda(), 1.0 / math.sqrt(128))
+    _check_o(o, oa.block_sparse_attn(q, k, v, mask))
+
+
+def test_golden_csp_case(K, golden_attention):
+    """The reference's reference_sparse_o output (bm=192, duplicate-free lists, one short list)."""
+    g = golden_attention
+    q, k, v = (g[f"csp_{n}"].bfloat16().cuda() for n in "qkv")
+    zero = torch.zeros_like(q)
+    o = K.csp_attn_fwd(q, k, v, g["csp_idx"].cuda(), g["csp_counts"].cuda(), zero, 1, int(g["csp_bm"]))
+    _check_o(o, g["csp_o"])
+
+
+@pytest.mark.parametrize("bm", [64, 128, 192, 256, 320])
+def test_csp_attn_matches_oracle(K, bm):
+    from oracle import attention as oa
+    B, H, Lq, Lkv, D = 2, 2, 700, 900, 128
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=bm)
+    G = (Lq + bm - 1) // bm
+    g = torch.Generator().manual_seed(bm)
+    cap = 384
+    idx = torch.randint(0, Lkv, (B, H, G, cap), generator=g, dtype=torch.int32)  # duplicates on purpose
+    counts = torch.randint(1, cap + 1, (B, H, G), generator=g, dtype=torch.int32)
+    counts[0, 0, 0] = 0      # empty list: delta = 0
+    counts[1, 1, -1] = cap   # full list
+    counts[0, 1, 0] = 128    # exactly one tile
+    o_in = torch.randn(B, H, Lq, D, generator=g).bfloat16()
+    for o_scale in (1, -1):
+        st = K.new_status("cuda")
+        o = K.csp_attn_fwd(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), counts.cuda(), o_in.cuda(), o_scale, bm,
+                           status=st)
+        _ok_status(K, st)
+        ref = oa.csp_attn(q, k, v, None, idx, counts, o_in, o_scale, bm=bm)
+        d = (o.float().cpu() - ref.float()).abs()
+        # one bf16 ulp of |o_in| + |delta| <= ~5 is 3.1e-2 at the very top of the range; typical error far lower
+        assert d.max().item() <= 3.2e-2 and d.mean().item() <= O_MEAN
+        rows0 = slice(0, min(bm, Lq))
+        assert torch.equal(o[0, 0, rows0].cpu(), o_in[0, 0, rows0]), "empty list must leave o untouched"
+
+
+def test_csp_attn_all_keys_equals_dense(K):
+    q, k, v = _qkv(1, 2, 512, 640, 64, seed=4)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    dense, _, _ = K.dense_attn_fwd(qc, kc, vc)
+    idx = torch.arange(640, dtype=torch.int32).expand(1, 2, 2, 640).contiguous().cuda()
+    counts = torch.full((1, 2, 2), 640, dtype=torch.int32, device="cuda")
+    o = K.csp_attn_fwd(qc, kc, vc, idx, counts, torch.zeros_like(qc), 1, 256)
+    assert (o.float() - dense.float()).abs().max().item() <= 8e-3
+
+
+def test_csp_attn_out_of_range_index_is_reported(K):
+    q, k, v = _qkv(1, 1, 128, 200, 64, seed=6)
+    idx = torch.arange(128, dtype=torch.int32).view(1, 1, 1, 128).clone()
+    idx[..., 5] = 10_000
+    counts = torch.full((1, 1, 1), 128, dtype=torch.int32)
+    st = K.new_status("cuda")
+    K.csp_attn_fwd(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), counts.cuda(), torch.zeros_like(q).cuda(), 1, 256,
+                   status=st)
+    assert K.read_status(st)[0] == 5
+
+
+def test_forced_wait_timeout_sets_status_and_context_survives(K):
+    """A wait limit of zero makes the first unfinished wait give up: the kernel must return, report
+    the status and leave the device usable (no trap, no hang)."""
+    q, k, v = _qkv(1, 2, 512, 2048, 128, seed=8)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    st = K.new_status("cuda")
+    K.dense_attn_fwd(qc, kc, vc, status=st, wait_limit_ns=0)
+    torch.cuda.synchronize()
+    assert K.read_status(st)[0] == 6
+    st2 = K.new_status("cuda")
+    o, _, _ = K.dense_attn_fwd(qc, kc, vc, status=st2)
+    _ok_status(K, st2)
+    ref = torch.nn.functional.scaled_dot_product_attention(qc, kc, vc)
+    assert (o.float() - ref.float()).abs().max().item() <= O_MAX
+
+
+def test_argument_errors(K):
+    from lvar_b200._lib import LvarError
+    q, k, v = (t.cuda() for t in _qkv(1, 1, 64, 64, 64))
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        K.dense_attn_fwd(q.float(), k, v)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        K.dense_attn_fwd(q.cpu(), k, v)
+    q96 = torch.randn(1, 1, 64, 96, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(LvarError, match="Head dimension must be 64 or 128"):
+        K.dense_attn_fwd(q96, q96, q96)
+    with pytest.raises(LvarError, match="scale"):
+        K.dense_attn_fwd(q, k, v, -1.0)
+    with pytest.raises(RuntimeError, match="mismatch"):
+        K.dense_attn_fwd(q, k[:, :, :32], v)
+
+
+# ----------------------------------------------------------------------------------------------
+# full-size checks through size-independent properties (Infinity-2B last scale: Lq 4096, Lkv 10521)
+# ----------------------------------------------------------------------------------------------
+def test_full_size_properties(K):
+    B, H, Lq, Lkv, D = 2, 16, 4096, 10521, 128
+    q, k, v = (t.cuda() for t in _qkv(B, H, Lq, Lkv, D, seed=0, peaked=True))
+    scale = 1.0 / math.sqrt(D)
+    dense, M, L = K.dense_attn_fwd(q, k, v, scale)
+    ref = torch.nn.functional.scaled_dot_product_attention(q[:1, :2], k[:1, :2], v[:1, :2], scale=scale)
+    assert (dense[:1, :2].float() - ref.float()).abs().max().item() <= O_MAX
+    # a block mask of all ones walks the same tiles in the same order as the dense kernel
+    ones = torch.ones(32, 83, dtype=torch.bool, device="cuda")
+    assert torch.equal(K.block_sparse_attn_fwd(q, k, v, ones, scale), dense)
+    # every softmax row sums to one => each group's column sums add up to the group's row count
+    cs = K.colsum_fwd(q, k, M, L, 256, scale)
+    assert cs.shape == (B, H, 16, Lkv)
+    assert torch.allclose(cs.sum(-1), torch.full((B, H, 16), 256.0, device="cuda"), rtol=1e-3)
+    assert (cs >= 0).all()
+    # group sums at two group sizes are consistent with each other
+    cs128 = K.colsum_fwd(q, k, M, L, 128, scale)
+    assert torch.allclose(cs128.view(B, H, 16, 2, Lkv).sum(3), cs, rtol=1e-4, atol=1e-6)
+    # the V path is linear, and scaling by a power of two is exact in bf16 and fp32:
+    # attention(q, k, 2v) == 2 * attention(q, k, v) bit for bit
+    a1 = K.block_sparse_attn_fwd(q[:1], k[:1], v[:1], ones, scale)
+    a2 = K.block_sparse_attn_fwd(q[:1], k[:1], (v[:1].float() * 2).bfloat16(), ones, scale)
+    assert torch.equal(a2.float(), a1.float() * 2)

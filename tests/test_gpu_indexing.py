@@ -1,0 +1,113 @@
+"""GPU mask / index construction against the CPU oracle: bit-exact for masks, lists and counts."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lvar_b200 import kernels
+    return kernels
+
+
+def _scores(shape, seed, ties=False):
+    g = torch.Generator().manual_seed(seed)
+    s = torch.rand(*shape, generator=g)
+    if ties:  # few distinct values => many equal scores, exercising the tie rule
+        s = torch.round(s * 16) / 16
+    return s
+
+
+@pytest.mark.parametrize("rows,n,k,ties", [
+    (3, 1, 1, False), (4, 7, 0, False), (5, 100, 100, True), (6, 1000, 192, False), (6, 1000, 192, True),
+    (2 * 2 * 3, 4121, 768, False), (4, 10521, 2176, True), (2, 24576, 2432, False), (3, 10521, 1052, True)])
+def test_topk_indices_bit_exact(K, rows, n, k, ties):
+    from oracle import indexing as oi
+    s = _scores((rows, n), seed=n + k, ties=ties)
+    s[0, : min(n, 3)] = -0.0 if ties else s[0, : min(n, 3)]
+    for asc in (False, True):
+        got, counts = K.topk_indices(s.cuda(), k, ascending_index=asc, out_cols=n, with_counts=True)
+        ref = oi.topk_indices(s, k, ascending_index=asc)
+        assert torch.equal(got[..., :k].cpu(), ref), f"asc={asc}"
+        assert (got[..., k:] == 0).all() and (counts == k).all()
+
+
+def test_topk_negative_and_special_values(K):
+    from oracle import indexing as oi
+    s = torch.tensor([[-1.0, -3.0, 0.0, -0.0, 2.5, float("inf"), -float("inf"), 2.5, 1e-38, -1e-38]])
+    for k in range(0, 11):
+        assert torch.equal(K.topk_indices(s.cuda(), k).cpu(), oi.topk_indices(s, k))
+
+
+def test_decision_step_indices_match_oracle(K):
+    """Decision-step list build: count, top-k by column sum, zero padding to Lkv columns."""
+    from lvar_b200 import policy as P
+    from oracle import indexing as oi
+    bs = _scores((2, 4, 7, 4121), seed=1)
+    count = P.indices_count(0.2, 4121, 128)
+    inds, counts = K.topk_indices(bs.cuda(), count, out_cols=4121, with_counts=True)
+    ref_i, ref_c = oi.decision_step_indices(bs, 0.2, 128, 4)
+    assert torch.equal(inds.cpu(), ref_i) and torch.equal(counts.cpu(), ref_c)
+
+
+@pytest.mark.parametrize("B,H,nq,nk,k_total,ties", [(2, 16, 32, 83, 17, False), (2, 4, 32, 83, 17, True),
+                                                    (1, 2, 128, 192, 19, True), (1, 1, 3, 5, 9, False),
+                                                    (2, 2, 4, 11, 6, True)])
+def test_build_block_mask_bit_exact(K, B, H, nq, nk, k_total, ties):
+    from lvar_b200 import policy as P
+    from oracle import indexing as oi
+    scores = _scores((B, H, nq, nk), seed=nq * nk, ties=ties)
+    always = P.sink_local_blocks(nq, nk, 128, 521 if nk > 8 else 128, (nk - nq) * 128 if nk > nq else 0)
+    mask, lists, counts = K.build_block_mask(scores.cuda(), always.cuda(), k_total, return_lists=True)
+    ref = oi.build_block_mask(scores, always, k_total)
+    assert torch.equal(mask.cpu(), ref)
+    assert torch.equal(counts.cpu(), ref.sum(-1).int())
+    want = max(k_total, int(always.sum(-1).max())) if k_total <= nk else nk
+    assert int(counts.max()) <= max(want, int(always.sum(-1).max()))
+    for b, h, i in ((0, 0, 0), (B - 1, H - 1, nq - 1)):
+        n = int(counts[b, h, i])
+        assert lists[b, h, i, :n].cpu().tolist() == torch.nonzero(ref[b, h, i]).flatten().tolist()
+        assert (lists[b, h, i, n:] == -1).all()
+    # no always-kept blocks at all
+    m2 = K.build_block_mask(scores.cuda(), None, min(3, nk))
+    assert torch.equal(m2.cpu(), oi.build_block_mask(scores, torch.zeros(nq, nk, dtype=torch.bool), min(3, nk)))
+
+
+def test_block_scores_match_oracle(K):
+    from oracle import indexing as oi
+    cs = _scores((2, 3, 5, 1000), seed=2) * 3
+    for block in (64, 128):
+        got = K.block_scores(cs.cuda(), block).cpu()
+        ref = oi.block_scores(cs, block).float()
+        assert got.shape == ref.shape
+        assert torch.allclose(got, ref, rtol=1e-6, atol=1e-6)
+        assert torch.equal(got, K.block_scores(cs.cuda(), block).cpu())
+
+
+@pytest.mark.parametrize("shape,mult,pad", [((1, 1, 1, 70), 4, 8), ((2, 3, 4, 1000), 64, 192), ((1, 2, 9, 4121), 112, 4),
+                                           ((1, 1, 2, 31), 1, 1), ((1, 1, 3, 64), 128, 64)])
+def test_mask_to_indices_matches_reference_order(K, shape, mult, pad):
+    from oracle import indexing as oi
+    g = torch.Generator().manual_seed(shape[-1])
+    m = torch.rand(*shape, generator=g) < 0.3
+    m[0, 0, 0] = False          # empty row: count 0
+    if shape[2] > 1:
+        m[0, 0, 1] = True       # full row: nothing to pad with
+    idx, cnt = K.mask_to_indices(m.cuda(), mult, pad)
+    ref_i, ref_c = oi.mask_to_indices(m, mult, pad)
+    assert idx.shape == ref_i.shape and torch.equal(cnt.cpu(), ref_c)
+    valid = ref_i >= 0
+    assert torch.equal(idx.cpu()[valid], ref_i[valid])
+
+
+def test_bitpack_roundtrip_and_layout(K):
+    from oracle import indexing as oi
+    g = torch.Generator().manual_seed(7)
+    for shape in ((1,), (9,), (3, 5, 7), (2, 16, 22, 1000)):
+        m = torch.rand(*shape, generator=g) < 0.5
+        packed, shp = K.bitpack(m.cuda())
+        assert torch.equal(packed.cpu(), oi.bitpack(m)[0])
+        assert torch.equal(K.bitunpack(packed, shp).cpu(), m)
