@@ -72,7 +72,6 @@ typedef struct lvar_attn_args {
   /* plumbing */
   int32_t* dev_status;    /* optional device int32, must be zeroed by the caller; see LVAR_DEV_* */
   uint64_t wait_limit_ns; /* per-wait limit of the kernel's bounded waits; 0 forces every pending wait to fail */
-  float* dbg;             /* optional device fp32 [128*128]: raw S of the first KV tile of CTA (0,0) */
 } lvar_attn_args;
 
 /* Dense attention o = softmax(q k^T * scale) v with row statistics.

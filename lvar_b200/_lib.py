@@ -51,7 +51,6 @@ class AttnArgs(C.Structure):
         ("o_scale", C.c_int32),
         ("dev_status", C.c_void_p),
         ("wait_limit_ns", C.c_uint64),
-        ("dbg", C.c_void_p),
     ]
 
 

@@ -8,6 +8,7 @@
 //   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp
 //   warp  9     V loader
 //   warp  10    allocates TMEM and issues every tcgen05.mma from one thread
+//   warp  11    idle; completes the fourth warpgroup so registers can be re-balanced (setmaxnreg)
 // TMEM (512 columns x 128 lanes, fp32): S0 | S1 | O0 | O1.  S_s = Q_s K^T lands in S_s; the softmax
 // warpgroup overwrites the first 64 columns of S_s with bf16 P_s, which is then the TMEM A operand of
 // O_s += P_s V.  Shared memory: Q0,Q1 + 2 K stages + 2 V stages, all 128-byte-swizzled [128][64]
@@ -30,7 +31,8 @@ namespace lvar {
 
 namespace {
 
-constexpr int kThreads = 352;
+constexpr int kThreads = 384;  // 8 softmax warps + K loader + V loader + MMA issuer + 1 idle warp
+constexpr int kRegsSoftmax = 208, kRegsOther = 72;
 constexpr int kMaxSteps = 2048;  // list capacity per CTA (KV tiles)
 constexpr int kStages = 2;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -65,7 +67,6 @@ struct AttnParams {
   // plumbing
   int* status;
   unsigned long long wait_limit_ns;
-  float* dbg;  // optional: raw S of the first step of CTA (0,0) slot 0, 128x128 fp32
 };
 
 template <int D>
@@ -119,6 +120,40 @@ __device__ __forceinline__ void gather_tile(uint32_t dst, const __nv_bfloat16* b
       kv = 0;
     }
     cp_async_16(dst + sw128_offset(r, c16), base + (int64_t)kv * row_stride + c16 * 8);
+  }
+}
+
+// max of a 32-element chunk of raw fp32 bits with 3-input max instructions
+__device__ __forceinline__ float chunk_max(const uint32_t (&r)[32]) {
+  float m0 = fmax3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+  float m1 = fmax3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
+#pragma unroll
+  for (int i = 6; i < 30; i += 4) {
+    m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+    m1 = fmax3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+  }
+  return fmax3(m0, m1, fmaxf(__uint_as_float(r[30]), __uint_as_float(r[31])));
+}
+
+// p = exp2(s * scale - m) for one 32-column chunk: packed FMA, row-sum accumulation in two packed
+// accumulators, bf16x2 packing of the 32 probabilities into pk[off .. off+15].
+__device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], uint64_t sc2, uint64_t nm2, uint64_t& sum_a,
+                                               uint64_t& sum_b, uint32_t (&pk)[32], int off) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
+    const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), sc2, nm2);
+    float a0, a1, b0, b1;
+    unpack_f32x2(t0, a0, a1);
+    unpack_f32x2(t1, b0, b1);
+    a0 = fast_exp2(a0);
+    a1 = fast_exp2(a1);
+    b0 = fast_exp2(b0);
+    b1 = fast_exp2(b1);
+    sum_a = fadd2(sum_a, pack_f32x2(a0, a1));
+    sum_b = fadd2(sum_b, pack_f32x2(b0, b1));
+    pk[off + i / 2] = pack_bf16x2(a0, a1);
+    pk[off + i / 2 + 1] = pack_bf16x2(b0, b1);
   }
 }
 
@@ -259,6 +294,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp < 8) {
     // ============================================================ softmax warpgroups
+    setmaxnreg_inc<kRegsSoftmax>();
     const int s = warp >> 2;
     const int quad = warp & 3;
     const int r_in_tile = quad * 32 + lane;
@@ -281,30 +317,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;  // warp-uniform: the TMEM accesses below are warp-collective
       tc_fence_after();
 
-      float sv[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(tS + c * 32, r);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]);
-      }
+      // raw fp32 bits of the S row, four 32-column chunks kept in registers
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld_x32(tS + 0, s0);
+      tmem_ld_x32(tS + 32, s1);
+      tmem_ld_x32(tS + 64, s2);
+      tmem_ld_x32(tS + 96, s3);
       tmem_wait_ld();
-
-      if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && s == 0 && it == 0) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) p.dbg[r_in_tile * 128 + i] = sv[i];
-      }
 
       const int valid = (MODE == MODE_CSP) ? (cnt_total - j * 128) : (p.Lkv - kvb * 128);
       if (valid < 128) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i >= valid) sv[i] = -INFINITY;
+        for (int i = 0; i < 32; ++i) {
+          if (i >= valid) s0[i] = 0xff800000u;  // -inf
+          if (i + 32 >= valid) s1[i] = 0xff800000u;
+          if (i + 64 >= valid) s2[i] = 0xff800000u;
+          if (i + 96 >= valid) s3[i] = 0xff800000u;
+        }
       }
-      float mx = sv[0];
-#pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, sv[i]);
+      const float mx = fmax3(fmaxf(chunk_max(s0), chunk_max(s1)), chunk_max(s2), chunk_max(s3));
       const float mx_s = mx * p.scale_log2;
       m_true = fmaxf(m_true, mx_s);
       const bool need = mx_s > m_ref + kRescaleThreshold;
@@ -316,34 +347,46 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         l *= alpha;
         if (it > 0) {
+          const uint64_t a2 = pack_f32x2(alpha, alpha);
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t r[32];
             tmem_ld_x32(tO + c * 32, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            for (int i = 0; i < 16; ++i) {
+              const uint64_t t = fmul2(pack_f32x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), a2);
+              float x0, x1;
+              unpack_f32x2(t, x0, x1);
+              r[2 * i] = __float_as_uint(x0);
+              r[2 * i + 1] = __float_as_uint(x1);
+            }
             tmem_st_x32(tO + c * 32, r);
           }
           tmem_wait_st();
         }
       }
-      const float neg_m = -m_ref;
-      float lsum0 = 0.f, lsum1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      const uint64_t nm2 = pack_f32x2(-m_ref, -m_ref);
+      uint64_t sum_a = 0ull, sum_b = 0ull;  // two packed accumulators = four partial row sums
+      {
         uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = fast_exp2(fmaf(sv[c * 64 + 2 * i], p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(sv[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
-          lsum0 += p0;
-          lsum1 += p1;
-          pk[i] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_x32(tS + c * 32, pk);
+        exp_pack_chunk(s0, sc2, nm2, sum_a, sum_b, pk, 0);
+        exp_pack_chunk(s1, sc2, nm2, sum_a, sum_b, pk, 16);
+        tmem_st_x32(tS, pk);
       }
-      l += lsum0 + lsum1;
+      {
+        uint32_t pk[32];
+        exp_pack_chunk(s2, sc2, nm2, sum_a, sum_b, pk, 0);
+        exp_pack_chunk(s3, sc2, nm2, sum_a, sum_b, pk, 16);
+        tmem_st_x32(tS + 32, pk);
+      }
+      {
+        float a0, a1, b0, b1;
+        unpack_f32x2(sum_a, a0, a1);
+        unpack_f32x2(sum_b, b0, b1);
+        l += (a0 + a1) + (b0 + b1);
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&bars->p_full[s]);
@@ -402,6 +445,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 8) {
     // ============================================================ K (and Q) loader
+    setmaxnreg_dec<kRegsOther>();
     int issued = 0;
     bool ok = true;
     if (MODE != MODE_CSP) {
@@ -474,6 +518,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (warp == 9) {
     // ============================================================ V loader
+    setmaxnreg_dec<kRegsOther>();
     bool ok = true;
     if (MODE != MODE_CSP) {
       if (lane == 0) {
@@ -525,8 +570,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
     __syncwarp();
-  } else {
-    // ============================================================ MMA issuer (warp 10, one thread)
+  } else if (warp == 10) {
+    // ============================================================ MMA issuer (one thread)
+    setmaxnreg_dec<kRegsOther>();
     if (lane == 0) {
       bool ok = mbar_wait(&bars->q_full, 0, wc, DEV_TIMEOUT_MMA);
       const uint32_t qaddr = smem_u32(sQ), kaddr = smem_u32(sK), vaddr = smem_u32(sV);
@@ -595,6 +641,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
     __syncwarp();
+  } else {
+    setmaxnreg_dec<kRegsOther>();  // idle warp: only takes part in the register re-balancing
   }
 
   // ---------------------------------------------------------------- teardown
@@ -672,7 +720,6 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   p.nkb = (a->Lkv + 127) / 128;
   p.status = a->dev_status;
   p.wait_limit_ns = a->wait_limit_ns;
-  p.dbg = a->dbg;
 
   dim3 grid;
   if (mode == MODE_BLOCK) {

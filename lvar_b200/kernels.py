@@ -57,7 +57,7 @@ def read_status(status: torch.Tensor) -> Tuple[int, str]:
     return code, _lib.DEV_STATUS_NAMES.get(code, f"unknown status {code}")
 
 
-def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None, dbg=None):
+def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None):
     """o = softmax(q k^T * scale) v; returns (o, M, L) with fp32 [B,H,Lq] statistics in base 2."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
@@ -74,8 +74,6 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
         a.dev_status = status.data_ptr()
     if wait_limit_ns is not None:
         a.wait_limit_ns = int(wait_limit_ns)
-    if dbg is not None:
-        a.dbg = dbg.data_ptr()
     check(lib.lvar_dense_attn(C.byref(a), _stream_ptr(q.device)))
     return o, M, L
 
