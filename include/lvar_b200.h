@@ -69,6 +69,13 @@ typedef struct lvar_attn_args {
   const void* o_in;   /* bf16 [B,H,Lq,D] accumulate input; may be the same buffer as o */
   int64_t oi_sb, oi_sh, oi_sl;
   int32_t o_scale; /* +1 or -1 */
+  /* scheduling: the kernels are persistent (one CTA per SM) and draw work items from a counter in
+   * device memory.  sched_scratch points to TWO int32 that are zero when the kernel starts; the kernel
+   * leaves them zero, so one zeroed buffer serves every later launch on the same stream.  Launches
+   * that may overlap on the GPU need separate buffers.  work_order (optional, int32[work items]) is
+   * the order in which items are handed out, e.g. heaviest first. */
+  int32_t* sched_scratch;
+  const int32_t* work_order;
   /* plumbing */
   int32_t* dev_status;    /* optional device int32, must be zeroed by the caller; see LVAR_DEV_* */
   uint64_t wait_limit_ns; /* per-wait limit of the kernel's bounded waits; 0 forces every pending wait to fail */

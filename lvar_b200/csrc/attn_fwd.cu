@@ -1,8 +1,10 @@
 // Attention forward for sm_100a: dense, block-sparse (128x128 block mask) and column-sparse
 // (token-index gather, "csp") variants of one warp-specialised tcgen05 kernel.
 //
-// One CTA owns two 128-row query tiles ("slots") of one (batch, head) and walks one list of
-// 128-key KV tiles; each list entry says which of the two slots uses the tile.
+// The kernel is persistent (one CTA per SM, work items drawn from a global counter).  A work item is
+// two 128-row query tiles ("slots") of one (batch, head); each slot walks its own ascending list of
+// 128-key KV tiles, the two lists advance in lock step ("rounds") and a tile both slots need in the
+// same round is loaded once (always the case for dense and column-sparse attention).
 //   warps 0-3   softmax warpgroup of slot 0 (thread = one query row = one TMEM lane)
 //   warps 4-7   softmax warpgroup of slot 1
 //   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp
@@ -33,8 +35,9 @@ namespace {
 
 constexpr int kThreads = 384;  // 8 softmax warps + K loader + V loader + MMA issuer + 1 idle warp
 constexpr int kRegsSoftmax = 208, kRegsOther = 72;
-constexpr int kMaxSteps = 2048;  // list capacity per CTA (KV tiles)
+constexpr int kMaxSteps = 1024;  // per-slot KV tile list capacity (block-sparse: Lkv <= 131072)
 constexpr int kStages = 2;
+constexpr int kSchedStages = 2;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2 };
@@ -64,6 +67,11 @@ struct AttnParams {
   const __nv_bfloat16* o_in;  // accumulate input (may alias o)
   int64_t oi_sb, oi_sh, oi_sl;
   float o_scale;
+  // persistent scheduling
+  int n_x;            // work items per (batch, head)
+  int total_items;
+  int* sched_counter;  // device int32[2], zero on entry and left zero on exit
+  const int32_t* work_order;  // optional permutation of the work items (heaviest first)
   // plumbing
   int* status;
   unsigned long long wait_limit_ns;
@@ -79,20 +87,35 @@ struct Smem {
   // aux: barriers then scalars then the step list
   static constexpr int kBarBytes = 256;
   static constexpr int kList = kAux + kBarBytes;
-  static constexpr int kTotal = kList + kMaxSteps * 2;
+  static constexpr int kTotal = kList + kSchedStages * 2 * kMaxSteps * 2;  // [stage][slot][kMaxSteps] uint16
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
+struct SchedEntry {
+  int item;  // work item id, < 0: no more work
+  int n0;    // KV tiles of slot 0
+  int n1;    // KV tiles of slot 1
+  int aux;   // csp: length of the item's index list
+};
+
+// One round of the two slots' tile streams: slot s works on KV tile kvb[s] if has[s]; when both want
+// the same tile it is loaded once and shared.
+struct Round {
+  bool has[2];
+  bool shared;
+  int kvb[2];
+};
+
 struct Bars {
-  uint64_t q_full;
+  uint64_t q_full, q_empty;
   uint64_t k_full[kStages], k_empty[kStages];
   uint64_t v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
+  uint64_t sched_full[kSchedStages], sched_empty[kSchedStages];
   uint64_t mma_done;
+  SchedEntry sched[kSchedStages];
   uint32_t tmem_base;
   int abort_flag;
-  int n_steps;
-  int n_act[2];
 };
 static_assert(sizeof(Bars) <= 256, "barrier block too large");
 
@@ -173,37 +196,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Bars* bars = reinterpret_cast<Bars*>(smem + SM::kAux);
-  uint16_t* list = reinterpret_cast<uint16_t*>(smem + SM::kList);
+  uint16_t* lists = reinterpret_cast<uint16_t*>(smem + SM::kList);  // [kSchedStages][kMaxSteps]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int b = bh / p.H;
-  const int h = bh % p.H;
-
-  // Row ranges of the two slots.
-  int row0[2], row_end[2];
-  int group = 0;
-  if (MODE == MODE_CSP) {
-    group = blockIdx.x / p.chunks_per_group;
-    const int chunk = blockIdx.x % p.chunks_per_group;
-    const int gend = min(p.Lq, (group + 1) * p.bm);
-    row0[0] = group * p.bm + chunk * 256;
-    row0[1] = row0[0] + 128;
-    row_end[0] = gend;
-    row_end[1] = gend;
-  } else {
-    row0[0] = blockIdx.x * 256;
-    row0[1] = row0[0] + 128;
-    row_end[0] = p.Lq;
-    row_end[1] = p.Lq;
-  }
-  const bool slot_live[2] = {row0[0] < row_end[0], row0[1] < row_end[1]};
 
   // ---------------------------------------------------------------- setup
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars->k_full[i], MODE == MODE_CSP ? 32 : 1);
       mbar_init(&bars->k_empty[i], 1);
@@ -214,6 +216,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->p_full[s], 128);
       mbar_init(&bars->o_full[s], 1);
+      mbar_init(&bars->o_empty[s], 128);
+    }
+    for (int i = 0; i < kSchedStages; ++i) {
+      mbar_init(&bars->sched_full[i], 1);
+      mbar_init(&bars->sched_empty[i], 11);  // 8 softmax warps + K loader + V loader + MMA issuer
     }
     mbar_init(&bars->mma_done, 1);
     bars->abort_flag = 0;
@@ -230,62 +237,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmV);
     }
   }
-  // Step list: entry = kv tile index | (slot bits << 14).
-  if (warp == 0) {
-    int n = 0, a0 = 0, a1 = 0;
-    if (MODE == MODE_BLOCK) {
-      const int qb0 = blockIdx.x * 2;
-      const uint8_t* m0 = p.mask + b * p.m_sb + h * p.m_sh + (int64_t)qb0 * p.m_sq;
-      const uint8_t* m1 = m0 + p.m_sq;
-      for (int base = 0; base < p.nkb; base += 32) {
-        const int j = base + lane;
-        uint32_t bits = 0;
-        if (j < p.nkb) {
-          if (slot_live[0] && m0[j]) bits |= 1u;
-          if (slot_live[1] && m1[j]) bits |= 2u;
-        }
-        const uint32_t vote = __ballot_sync(0xffffffffu, bits != 0);
-        const int pos = n + __popc(vote & ((1u << lane) - 1u));
-        if (bits && pos < kMaxSteps) list[pos] = (uint16_t)(j | (bits << 14));
-        n += __popc(vote);
-        a0 += __popc(__ballot_sync(0xffffffffu, bits & 1u));
-        a1 += __popc(__ballot_sync(0xffffffffu, bits & 2u));
-      }
-    } else if (MODE == MODE_DENSE) {
-      n = p.nkb;
-      a0 = slot_live[0] ? n : 0;
-      a1 = slot_live[1] ? n : 0;
-    } else {
-      const int cnt = p.counts[b * p.c_sb + h * p.c_sh + group];
-      n = (cnt + 127) / 128;
-      a0 = slot_live[0] ? n : 0;
-      a1 = slot_live[1] ? n : 0;
-    }
-    if (!slot_live[0] && !slot_live[1]) n = 0;  // chunk past the end of its query group: nothing to do
-    if (lane == 0) {
-      bars->n_steps = (MODE == MODE_BLOCK) ? min(n, kMaxSteps) : n;
-      bars->n_act[0] = a0;
-      bars->n_act[1] = a1;
-    }
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
 
   const uint32_t tmem_base = bars->tmem_base;
-  const int n_steps = bars->n_steps;
-  const uint32_t dense_bits = (slot_live[0] ? 1u : 0u) | (slot_live[1] ? 2u : 0u);
   WaitCtx wc{p.status, &bars->abort_flag, p.wait_limit_ns};
 
-  auto get_step = [&](int j, int& kvb, uint32_t& bits) {
-    if (MODE == MODE_BLOCK) {
-      const uint16_t e = list[j];
-      kvb = e & 0x3FFF;
-      bits = e >> 14;
+  // A work item is one (batch, head) x (pair of 128-row query tiles).  Decoded by every role itself.
+  struct Item {
+    int b, h, bh, group;
+    int row0[2], row_end[2];
+    uint32_t live;  // bit s: slot s has at least one query row
+  };
+  auto decode = [&](int item) {
+    Item it;
+    it.bh = item / p.n_x;
+    const int x = item % p.n_x;
+    it.b = it.bh / p.H;
+    it.h = it.bh % p.H;
+    it.group = 0;
+    int gend = p.Lq;
+    if (MODE == MODE_CSP) {
+      it.group = x / p.chunks_per_group;
+      const int chunk = x % p.chunks_per_group;
+      gend = min(p.Lq, (it.group + 1) * p.bm);
+      it.row0[0] = it.group * p.bm + chunk * 256;
     } else {
-      kvb = j;
-      bits = dense_bits;
+      it.row0[0] = x * 256;
     }
+    it.row0[1] = it.row0[0] + 128;
+    it.row_end[0] = it.row_end[1] = gend;
+    it.live = (it.row0[0] < gend ? 1u : 0u) | (it.row0[1] < gend ? 2u : 0u);
+    return it;
+  };
+  auto round_info = [&](const uint16_t* l0, const uint16_t* l1, const SchedEntry& e, int r) {
+    Round rd;
+    rd.has[0] = r < e.n0;
+    rd.has[1] = r < e.n1;
+    if (MODE == MODE_BLOCK) {
+      rd.kvb[0] = rd.has[0] ? l0[r] : 0;
+      rd.kvb[1] = rd.has[1] ? l1[r] : 0;
+    } else {
+      rd.kvb[0] = rd.kvb[1] = r;
+    }
+    rd.shared = rd.has[0] && rd.has[1] && rd.kvb[0] == rd.kvb[1];
+    return rd;
+  };
+  // Waits for the n-th schedule entry of this CTA; false on abort.
+  auto acquire_item = [&](int n, SchedEntry& e, int code) {
+    const int slot = n % kSchedStages;
+    if (!mbar_wait(&bars->sched_full[slot], (n / kSchedStages) & 1, wc, code)) return false;
+    e = bars->sched[slot];
+    return true;
   };
 
   uint8_t* sQ = smem + SM::kQ;
@@ -298,109 +302,121 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int s = warp >> 2;
     const int quad = warp & 3;
     const int r_in_tile = quad * 32 + lane;
-    const int row = row0[s] + r_in_tile;
-    const bool row_ok = row < row_end[s];
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const uint32_t tS = tmem_base + lane_off + (uint32_t)s * 128u;
     const uint32_t tO = tmem_base + lane_off + TM_O + (uint32_t)s * D;
-    const int cnt_total = (MODE == MODE_CSP) ? p.counts[b * p.c_sb + h * p.c_sh + group] : 0;
-
-    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
-    int it = 0;
+    int n_s = 0;  // S tiles consumed by this slot so far (parity of s_full)
+    int n_o = 0;  // items in which this slot produced an output (parity of o_full)
     bool ok = true;
-    for (int j = 0; j < n_steps; ++j) {
-      int kvb;
-      uint32_t bits;
-      get_step(j, kvb, bits);
-      if (!((bits >> s) & 1u)) continue;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], it & 1, wc, DEV_TIMEOUT_SOFTMAX));
-      if (!ok) break;  // warp-uniform: the TMEM accesses below are warp-collective
-      tc_fence_after();
 
-      // raw fp32 bits of the S row, four 32-column chunks kept in registers
-      uint32_t s0[32], s1[32], s2[32], s3[32];
-      tmem_ld_x32(tS + 0, s0);
-      tmem_ld_x32(tS + 32, s1);
-      tmem_ld_x32(tS + 64, s2);
-      tmem_ld_x32(tS + 96, s3);
-      tmem_wait_ld();
+    for (int n = 0; ok; ++n) {
+      SchedEntry e;
+      ok = __all_sync(0xffffffffu, acquire_item(n, e, DEV_TIMEOUT_SOFTMAX));
+      if (!ok || e.item < 0) break;
+      const Item im = decode(e.item);
+      const uint16_t* mylist = lists + ((n % kSchedStages) * 2 + s) * kMaxSteps;
+      const int row = im.row0[s] + r_in_tile;
+      const bool row_ok = row < im.row_end[s];
+      const int cnt_total = (MODE == MODE_CSP) ? e.aux : 0;
+      const int n_mine = s == 0 ? e.n0 : e.n1;
 
-      const int valid = (MODE == MODE_CSP) ? (cnt_total - j * 128) : (p.Lkv - kvb * 128);
-      if (valid < 128) {
+      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      int it = 0;
+      for (int j = 0; j < n_mine; ++j) {
+        const int kvb = (MODE == MODE_BLOCK) ? mylist[j] : j;
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, wc, DEV_TIMEOUT_SOFTMAX));
+        if (!ok) break;  // warp-uniform: the TMEM accesses below are warp-collective
+        ++n_s;
+        tc_fence_after();
+
+        // raw fp32 bits of the S row, four 32-column chunks kept in registers
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld_x32(tS + 0, s0);
+        tmem_ld_x32(tS + 32, s1);
+        tmem_ld_x32(tS + 64, s2);
+        tmem_ld_x32(tS + 96, s3);
+        tmem_wait_ld();
+
+        const int valid = (MODE == MODE_CSP) ? (cnt_total - j * 128) : (p.Lkv - kvb * 128);
+        if (valid < 128) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (i >= valid) s0[i] = 0xff800000u;  // -inf
-          if (i + 32 >= valid) s1[i] = 0xff800000u;
-          if (i + 64 >= valid) s2[i] = 0xff800000u;
-          if (i + 96 >= valid) s3[i] = 0xff800000u;
-        }
-      }
-      const float mx = fmax3(fmaxf(chunk_max(s0), chunk_max(s1)), chunk_max(s2), chunk_max(s3));
-      const float mx_s = mx * p.scale_log2;
-      m_true = fmaxf(m_true, mx_s);
-      const bool need = mx_s > m_ref + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, need)) {
-        float alpha = 1.0f;
-        if (need) {
-          alpha = fast_exp2(m_ref - mx_s);
-          m_ref = mx_s;
-        }
-        l *= alpha;
-        if (it > 0) {
-          const uint64_t a2 = pack_f32x2(alpha, alpha);
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_x32(tO + c * 32, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const uint64_t t = fmul2(pack_f32x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), a2);
-              float x0, x1;
-              unpack_f32x2(t, x0, x1);
-              r[2 * i] = __float_as_uint(x0);
-              r[2 * i + 1] = __float_as_uint(x1);
-            }
-            tmem_st_x32(tO + c * 32, r);
+          for (int i = 0; i < 32; ++i) {
+            if (i >= valid) s0[i] = 0xff800000u;  // -inf
+            if (i + 32 >= valid) s1[i] = 0xff800000u;
+            if (i + 64 >= valid) s2[i] = 0xff800000u;
+            if (i + 96 >= valid) s3[i] = 0xff800000u;
           }
-          tmem_wait_st();
         }
+        const float mx = fmax3(fmaxf(chunk_max(s0), chunk_max(s1)), chunk_max(s2), chunk_max(s3));
+        const float mx_s = mx * p.scale_log2;
+        m_true = fmaxf(m_true, mx_s);
+        const bool need = mx_s > m_ref + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          float alpha = 1.0f;
+          if (need) {
+            alpha = fast_exp2(m_ref - mx_s);
+            m_ref = mx_s;
+          }
+          l *= alpha;
+          if (it > 0) {
+            const uint64_t a2 = pack_f32x2(alpha, alpha);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_x32(tO + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const uint64_t t = fmul2(pack_f32x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), a2);
+                float x0, x1;
+                unpack_f32x2(t, x0, x1);
+                r[2 * i] = __float_as_uint(x0);
+                r[2 * i + 1] = __float_as_uint(x1);
+              }
+              tmem_st_x32(tO + c * 32, r);
+            }
+            tmem_wait_st();
+          }
+        }
+        const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+        const uint64_t nm2 = pack_f32x2(-m_ref, -m_ref);
+        uint64_t sum_a = 0ull, sum_b = 0ull;  // two packed accumulators = four partial row sums
+        {
+          uint32_t pk[32];
+          exp_pack_chunk(s0, sc2, nm2, sum_a, sum_b, pk, 0);
+          exp_pack_chunk(s1, sc2, nm2, sum_a, sum_b, pk, 16);
+          tmem_st_x32(tS, pk);
+        }
+        {
+          uint32_t pk[32];
+          exp_pack_chunk(s2, sc2, nm2, sum_a, sum_b, pk, 0);
+          exp_pack_chunk(s3, sc2, nm2, sum_a, sum_b, pk, 16);
+          tmem_st_x32(tS + 32, pk);
+        }
+        {
+          float a0, a1, b0, b1;
+          unpack_f32x2(sum_a, a0, a1);
+          unpack_f32x2(sum_b, b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[s]);
+        ++it;
       }
-      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
-      const uint64_t nm2 = pack_f32x2(-m_ref, -m_ref);
-      uint64_t sum_a = 0ull, sum_b = 0ull;  // two packed accumulators = four partial row sums
-      {
-        uint32_t pk[32];
-        exp_pack_chunk(s0, sc2, nm2, sum_a, sum_b, pk, 0);
-        exp_pack_chunk(s1, sc2, nm2, sum_a, sum_b, pk, 16);
-        tmem_st_x32(tS, pk);
-      }
-      {
-        uint32_t pk[32];
-        exp_pack_chunk(s2, sc2, nm2, sum_a, sum_b, pk, 0);
-        exp_pack_chunk(s3, sc2, nm2, sum_a, sum_b, pk, 16);
-        tmem_st_x32(tS + 32, pk);
-      }
-      {
-        float a0, a1, b0, b1;
-        unpack_f32x2(sum_a, a0, a1);
-        unpack_f32x2(sum_b, b0, b1);
-        l += (a0 + a1) + (b0 + b1);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bars->p_full[s]);
-      ++it;
-    }
+      if (!ok) break;
 
-    // ---- epilogue: O / l -> bf16 -> global; row statistics
-    if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], 0, wc, DEV_TIMEOUT_SOFTMAX));
-    if (ok) {
-      tc_fence_after();
+      // ---- epilogue: O / l -> bf16 -> global; row statistics
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, wc, DEV_TIMEOUT_SOFTMAX));
+        if (!ok) break;
+        ++n_o;
+        tc_fence_after();
+      }
       const float inv_l = (it > 0) ? (1.0f / l) : 0.f;
-      __nv_bfloat16* orow = p.o + b * p.o_sb + h * p.o_sh + (int64_t)row * p.o_sl;
+      __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
       const __nv_bfloat16* irow =
-          (MODE == MODE_CSP) ? (p.o_in + b * p.oi_sb + h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
+          (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -410,6 +426,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (c == D / 32 - 1 && it > 0) {
+          // O has been read out of TMEM: the MMA warp may overwrite it for the next item
+          tc_fence_before();
+          mbar_arrive(&bars->o_empty[s]);
         }
         if (row_ok) {
 #pragma unroll
@@ -438,80 +459,101 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       if (row_ok && MODE != MODE_CSP) {
-        const int64_t si = (int64_t)bh * p.Lq + row;
+        const int64_t si = (int64_t)im.bh * p.Lq + row;
         if (p.M) p.M[si] = m_true;
         if (p.L) p.L[si] = (it > 0) ? l * fast_exp2(m_ref - m_true) : 0.f;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
     }
   } else if (warp == 8) {
     // ============================================================ K (and Q) loader
     setmaxnreg_dec<kRegsOther>();
-    int issued = 0;
     bool ok = true;
-    if (MODE != MODE_CSP) {
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&bars->q_full, 2 * SM::kTile);
-        for (int s = 0; s < 2; ++s)
-          for (int sub = 0; sub < NSUB; ++sub)
-            tma_load_4d(sQ + s * SM::kTile + sub * 16384, &tmQ, &bars->q_full, sub * 64, row0[s], h, b);
-        for (int j = 0; j < n_steps; ++j) {
-          int kvb;
-          uint32_t bits;
-          get_step(j, kvb, bits);
-          const int st = j % kStages;
-          ok = mbar_wait(&bars->k_empty[st], ((j / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&bars->k_full[st], SM::kTile);
-          for (int sub = 0; sub < NSUB; ++sub)
-            tma_load_4d(sK + st * SM::kTile + sub * 16384, &tmK, &bars->k_full[st], sub * 64, kvb * 128, h, b);
-          issued = j + 1;
-        }
-        // Drain on abort: copies in flight must land before the CTA's shared memory is released.
-        if (bars->abort_flag) {
-          const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try_wait(&bars->q_full, 0) && globaltimer_ns() - t0 < 2000000000ull) {
-          }
-          for (int j = max(0, issued - kStages); j < issued; ++j) {
-            const int st = j % kStages;
-            const uint64_t t1 = globaltimer_ns();
-            while (!mbar_try_wait(&bars->k_full[st], (j / kStages) & 1) && globaltimer_ns() - t1 < 2000000000ull) {
+    int kc = 0;       // K tiles issued so far (stage = kc % kStages)
+    int nq_items = 0; // items with at least one step (parity of q_full / q_empty)
+    int pending = -1; // csp: stage whose cp.async group has been committed but not yet signalled
+    const bool issuer = (MODE == MODE_CSP) || lane == 0;
+    if (issuer) {
+      for (int n = 0; ok; ++n) {
+        SchedEntry e;
+        ok = acquire_item(n, e, DEV_TIMEOUT_PRODUCER);
+        if (MODE == MODE_CSP) ok = __all_sync(0xffffffffu, ok);
+        if (!ok || e.item < 0) break;
+        const Item im = decode(e.item);
+        const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
+        const uint16_t* l1 = l0 + kMaxSteps;
+        const int rounds = max(e.n0, e.n1);
+        if (rounds > 0) {
+          if (lane == 0) {
+            ok = mbar_wait(&bars->q_empty, (nq_items & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
+            if (ok) {
+              mbar_arrive_expect_tx(&bars->q_full, 2 * SM::kTile);
+              for (int s = 0; s < 2; ++s)
+                for (int sub = 0; sub < NSUB; ++sub)
+                  tma_load_4d(sQ + s * SM::kTile + sub * 16384, &tmQ, &bars->q_full, sub * 64, im.row0[s], im.h, im.b);
             }
           }
+          if (MODE == MODE_CSP) ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ++nq_items;
         }
-      }
-    } else {
-      // csp: Q by TMA (lane 0), K rows gathered by the whole warp with 16-byte cp.async.
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&bars->q_full, 2 * SM::kTile);
-        for (int s = 0; s < 2; ++s)
-          for (int sub = 0; sub < NSUB; ++sub)
-            tma_load_4d(sQ + s * SM::kTile + sub * 16384, &tmQ, &bars->q_full, sub * 64, row0[s], h, b);
-      }
-      const int32_t* idx = p.indices + b * p.i_sb + h * p.i_sh + (int64_t)group * p.i_sg;
-      const int cnt = p.counts[b * p.c_sb + h * p.c_sh + group];
-      const __nv_bfloat16* kbase = p.k + b * p.k_sb + h * p.k_sh;
-      for (int j = 0; j < n_steps; ++j) {
-        const int st = j % kStages;
-        ok = mbar_wait(&bars->k_empty[st], ((j / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
-        ok = __all_sync(0xffffffffu, ok);
+        if (MODE != MODE_CSP) {
+          for (int r = 0; r < rounds && ok; ++r) {
+            const Round rd = round_info(l0, l1, e, r);
+            for (int s = 0; s < 2; ++s) {
+              if (!rd.has[s] || (s == 1 && rd.shared)) continue;
+              const int st = kc % kStages;
+              ok = mbar_wait(&bars->k_empty[st], ((kc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
+              if (!ok) break;
+              mbar_arrive_expect_tx(&bars->k_full[st], SM::kTile);
+              for (int sub = 0; sub < NSUB; ++sub)
+                tma_load_4d(sK + st * SM::kTile + sub * 16384, &tmK, &bars->k_full[st], sub * 64, rd.kvb[s] * 128, im.h,
+                            im.b);
+              ++kc;
+            }
+          }
+        } else {
+          const int32_t* idx = p.indices + im.b * p.i_sb + im.h * p.i_sh + (int64_t)im.group * p.i_sg;
+          const __nv_bfloat16* kbase = p.k + im.b * p.k_sb + im.h * p.k_sh;
+          for (int j = 0; j < rounds; ++j) {
+            const int st = kc % kStages;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_empty[st], ((kc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
+            if (!ok) break;
+            gather_tile<D>(smem_u32(sK + st * SM::kTile), kbase, p.k_sl, idx, e.aux, j, p.Lkv, lane, p.status);
+            cp_async_commit();
+            if (pending >= 0) {  // the previous tile has landed once at most one group is pending
+              cp_async_wait<1>();
+              fence_proxy_async_smem();
+              mbar_arrive(&bars->k_full[pending]);
+            }
+            pending = st;
+            ++kc;
+          }
+          if (pending >= 0) {
+            cp_async_wait<0>();
+            fence_proxy_async_smem();
+            mbar_arrive(&bars->k_full[pending]);
+            pending = -1;
+          }
+        }
         if (!ok) break;
-        gather_tile<D>(smem_u32(sK + st * SM::kTile), kbase, p.k_sl, idx, cnt, j, p.Lkv, lane, p.status);
-        cp_async_commit();
-        issued = j + 1;
-        if (j > 0) {  // tile j-1 has landed once at most one group is still pending
-          cp_async_wait<1>();
-          fence_proxy_async_smem();
-          mbar_arrive(&bars->k_full[(j - 1) % kStages]);
-        }
+        if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
       }
-      cp_async_wait<0>();  // also drains on abort
-      if (issued > 0 && ok) {
-        fence_proxy_async_smem();
-        mbar_arrive(&bars->k_full[(issued - 1) % kStages]);
-      }
+      if (MODE == MODE_CSP) cp_async_wait<0>();  // drains on abort too
+      // Drain on abort: copies in flight must land before the CTA's shared memory is released.
       if (lane == 0 && bars->abort_flag) {
         const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(&bars->q_full, 0) && globaltimer_ns() - t0 < 2000000000ull) {
+        if (nq_items > 0)
+          while (!mbar_try_wait(&bars->q_full, (nq_items - 1) & 1) && globaltimer_ns() - t0 < 2000000000ull) {
+          }
+        if (MODE != MODE_CSP) {
+          for (int c = max(0, kc - kStages); c < kc; ++c) {
+            const uint64_t t1 = globaltimer_ns();
+            while (!mbar_try_wait(&bars->k_full[c % kStages], (c / kStages) & 1) &&
+                   globaltimer_ns() - t1 < 2000000000ull) {
+            }
+          }
         }
       }
     }
@@ -520,53 +562,69 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ============================================================ V loader
     setmaxnreg_dec<kRegsOther>();
     bool ok = true;
-    if (MODE != MODE_CSP) {
-      if (lane == 0) {
-        int issued = 0;
-        for (int j = 0; j < n_steps; ++j) {
-          int kvb;
-          uint32_t bits;
-          get_step(j, kvb, bits);
-          const int st = j % kStages;
-          ok = mbar_wait(&bars->v_empty[st], ((j / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&bars->v_full[st], SM::kTile);
-          for (int sub = 0; sub < NSUB; ++sub)
-            tma_load_4d(sV + st * SM::kTile + sub * 16384, &tmV, &bars->v_full[st], sub * 64, kvb * 128, h, b);
-          issued = j + 1;
-        }
-        if (bars->abort_flag) {
-          for (int j = max(0, issued - kStages); j < issued; ++j) {
-            const int st = j % kStages;
-            const uint64_t t1 = globaltimer_ns();
-            while (!mbar_try_wait(&bars->v_full[st], (j / kStages) & 1) && globaltimer_ns() - t1 < 2000000000ull) {
+    int vc = 0;
+    int pending = -1;
+    const bool issuer = (MODE == MODE_CSP) || lane == 0;
+    if (issuer) {
+      for (int n = 0; ok; ++n) {
+        SchedEntry e;
+        ok = acquire_item(n, e, DEV_TIMEOUT_PRODUCER);
+        if (MODE == MODE_CSP) ok = __all_sync(0xffffffffu, ok);
+        if (!ok || e.item < 0) break;
+        const Item im = decode(e.item);
+        const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
+        const uint16_t* l1 = l0 + kMaxSteps;
+        const int rounds = max(e.n0, e.n1);
+        if (MODE != MODE_CSP) {
+          for (int r = 0; r < rounds && ok; ++r) {
+            const Round rd = round_info(l0, l1, e, r);
+            for (int s = 0; s < 2; ++s) {
+              if (!rd.has[s] || (s == 1 && rd.shared)) continue;
+              const int st = vc % kStages;
+              ok = mbar_wait(&bars->v_empty[st], ((vc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
+              if (!ok) break;
+              mbar_arrive_expect_tx(&bars->v_full[st], SM::kTile);
+              for (int sub = 0; sub < NSUB; ++sub)
+                tma_load_4d(sV + st * SM::kTile + sub * 16384, &tmV, &bars->v_full[st], sub * 64, rd.kvb[s] * 128, im.h,
+                            im.b);
+              ++vc;
             }
           }
+        } else {
+          const int32_t* idx = p.indices + im.b * p.i_sb + im.h * p.i_sh + (int64_t)im.group * p.i_sg;
+          const __nv_bfloat16* vbase = p.v + im.b * p.v_sb + im.h * p.v_sh;
+          for (int j = 0; j < rounds; ++j) {
+            const int st = vc % kStages;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_empty[st], ((vc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
+            if (!ok) break;
+            gather_tile<D>(smem_u32(sV + st * SM::kTile), vbase, p.v_sl, idx, e.aux, j, p.Lkv, lane, nullptr);
+            cp_async_commit();
+            if (pending >= 0) {
+              cp_async_wait<1>();
+              fence_proxy_async_smem();
+              mbar_arrive(&bars->v_full[pending]);
+            }
+            pending = st;
+            ++vc;
+          }
+          if (pending >= 0) {
+            cp_async_wait<0>();
+            fence_proxy_async_smem();
+            mbar_arrive(&bars->v_full[pending]);
+            pending = -1;
+          }
         }
-      }
-    } else {
-      const int32_t* idx = p.indices + b * p.i_sb + h * p.i_sh + (int64_t)group * p.i_sg;
-      const int cnt = p.counts[b * p.c_sb + h * p.c_sh + group];
-      const __nv_bfloat16* vbase = p.v + b * p.v_sb + h * p.v_sh;
-      int issued = 0;
-      for (int j = 0; j < n_steps; ++j) {
-        const int st = j % kStages;
-        ok = mbar_wait(&bars->v_empty[st], ((j / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER);
-        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        gather_tile<D>(smem_u32(sV + st * SM::kTile), vbase, p.v_sl, idx, cnt, j, p.Lkv, lane, nullptr);
-        cp_async_commit();
-        issued = j + 1;
-        if (j > 0) {  // tile j-1 has landed once at most one group is still pending
-          cp_async_wait<1>();
-          fence_proxy_async_smem();
-          mbar_arrive(&bars->v_full[(j - 1) % kStages]);
-        }
+        if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
       }
-      cp_async_wait<0>();  // also drains on abort
-      if (issued > 0 && ok) {
-        fence_proxy_async_smem();
-        mbar_arrive(&bars->v_full[(issued - 1) % kStages]);
+      if (MODE == MODE_CSP) cp_async_wait<0>();
+      if (MODE != MODE_CSP && lane == 0 && bars->abort_flag) {
+        for (int c = max(0, vc - kStages); c < vc; ++c) {
+          const uint64_t t1 = globaltimer_ns();
+          while (!mbar_try_wait(&bars->v_full[c % kStages], (c / kStages) & 1) &&
+                 globaltimer_ns() - t1 < 2000000000ull) {
+          }
+        }
       }
     }
     __syncwarp();
@@ -574,61 +632,103 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ============================================================ MMA issuer (one thread)
     setmaxnreg_dec<kRegsOther>();
     if (lane == 0) {
-      bool ok = mbar_wait(&bars->q_full, 0, wc, DEV_TIMEOUT_MMA);
+      bool ok = true;
       const uint32_t qaddr = smem_u32(sQ), kaddr = smem_u32(sK), vaddr = smem_u32(sV);
-      uint32_t prev_bits = 0;
-      int prev_st = 0, prev_j = 0;
-      int npv[2] = {0, 0};
-      for (int j = 0; j <= n_steps && ok; ++j) {
-        int kvb = 0;
-        uint32_t bits = 0;
-        if (j < n_steps) get_step(j, kvb, bits);
-        const int st = j % kStages;
-        if (bits) {
-          ok = mbar_wait(&bars->k_full[st], (j / kStages) & 1, wc, DEV_TIMEOUT_MMA);
+      int kc = 0, vc = 0;        // K / V tiles consumed so far
+      int nq_items = 0;          // items with steps (parity of q_full)
+      int n_p[2] = {0, 0};       // P tiles consumed per slot (parity of p_full)
+      int n_o[2] = {0, 0};       // items in which the slot produced an output (parity of o_empty)
+      for (int n = 0; ok; ++n) {
+        SchedEntry e;
+        ok = acquire_item(n, e, DEV_TIMEOUT_MMA);
+        if (!ok || e.item < 0) break;
+        const Item im = decode(e.item);
+        const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
+        const uint16_t* l1 = l0 + kMaxSteps;
+        const int rounds = max(e.n0, e.n1);
+        if (rounds > 0) {
+          ok = mbar_wait(&bars->q_full, nq_items & 1, wc, DEV_TIMEOUT_MMA);
           if (!ok) break;
+          ++nq_items;
         }
-        if (prev_bits) {
-          ok = mbar_wait(&bars->v_full[prev_st], (prev_j / kStages) & 1, wc, DEV_TIMEOUT_MMA);
+        Round prev;
+        prev.has[0] = prev.has[1] = prev.shared = false;
+        prev.kvb[0] = prev.kvb[1] = 0;
+        int pvs[2] = {0, 0}, pvp[2] = {0, 0};  // V stage / parity of the previous round, per slot
+        int npv[2] = {0, 0};
+        for (int r = 0; r <= rounds && ok; ++r) {
+          Round cur;
+          cur.has[0] = cur.has[1] = cur.shared = false;
+          cur.kvb[0] = cur.kvb[1] = 0;
+          if (r < rounds) cur = round_info(l0, l1, e, r);
+          // stages of this round's tiles (same order as the loaders issue them)
+          int ks[2] = {0, 0}, kp[2] = {0, 0}, vs[2] = {0, 0}, vp[2] = {0, 0};
+          for (int s = 0; s < 2; ++s) {
+            if (!cur.has[s]) continue;
+            if (s == 1 && cur.shared) {
+              ks[1] = ks[0]; kp[1] = kp[0]; vs[1] = vs[0]; vp[1] = vp[0];
+              continue;
+            }
+            ks[s] = kc % kStages; kp[s] = (kc / kStages) & 1; ++kc;
+            vs[s] = vc % kStages; vp[s] = (vc / kStages) & 1; ++vc;
+          }
+          for (int s = 0; s < 2 && ok; ++s) {
+            if (prev.has[s]) {
+              if (!(s == 1 && prev.shared)) {
+                ok = mbar_wait(&bars->v_full[pvs[s]], pvp[s], wc, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+              }
+              if (npv[s] == 0) {
+                // first PV of the item overwrites O_s: the previous item's epilogue must have read it
+                ok = mbar_wait(&bars->o_empty[s], (n_o[s] & 1) ^ 1, wc, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+              }
+              ok = mbar_wait(&bars->p_full[s], n_p[s] & 1, wc, DEV_TIMEOUT_MMA);
+              if (!ok) break;
+              ++n_p[s];
+              tc_fence_after();
+              const uint32_t tP = tmem_base + (uint32_t)s * 128u;
+              const uint32_t tOs = tmem_base + TM_O + (uint32_t)s * D;
+#pragma unroll
+              for (int ks8 = 0; ks8 < 8; ++ks8) {
+                const uint64_t bd = make_sw128_desc(vaddr + pvs[s] * SM::kTile + ks8 * 2048, 16384, 1024);
+                umma_ts(tOs, tP + ks8 * 8, bd, IDESC_PV, (npv[s] > 0 || ks8 > 0) ? 1u : 0u);
+              }
+              ++npv[s];
+              // release the V stage after its last user
+              if (!(s == 0 && prev.shared)) umma_commit(&bars->v_empty[pvs[s]]);
+            }
+            if (cur.has[s]) {
+              if (!(s == 1 && cur.shared)) {
+                ok = mbar_wait(&bars->k_full[ks[s]], kp[s], wc, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+                tc_fence_after();
+              }
+              const uint32_t tSs = tmem_base + (uint32_t)s * 128u;
+#pragma unroll
+              for (int kq = 0; kq < KSTEPS_QK; ++kq) {
+                const uint32_t koff = (kq >> 2) * 16384 + (kq & 3) * 32;
+                const uint64_t ad = make_sw128_desc(qaddr + s * SM::kTile + koff, 16, 1024);
+                const uint64_t bd = make_sw128_desc(kaddr + ks[s] * SM::kTile + koff, 16, 1024);
+                umma_ss(tSs, ad, bd, IDESC_QK, kq > 0 ? 1u : 0u);
+              }
+              umma_commit(&bars->s_full[s]);
+              if (!(s == 0 && cur.shared)) umma_commit(&bars->k_empty[ks[s]]);
+            }
+          }
           if (!ok) break;
-        }
-        tc_fence_after();
-        for (int s = 0; s < 2 && ok; ++s) {
-          if ((prev_bits >> s) & 1u) {
-            ok = mbar_wait(&bars->p_full[s], npv[s] & 1, wc, DEV_TIMEOUT_MMA);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t tP = tmem_base + (uint32_t)s * 128u;
-            const uint32_t tOs = tmem_base + TM_O + (uint32_t)s * D;
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              const uint64_t bd = make_sw128_desc(vaddr + prev_st * SM::kTile + ks * 2048, 16384, 1024);
-              umma_ts(tOs, tP + ks * 8, bd, IDESC_PV, (npv[s] > 0 || ks > 0) ? 1u : 0u);
-            }
-            ++npv[s];
-          }
-          if ((bits >> s) & 1u) {
-            const uint32_t tSs = tmem_base + (uint32_t)s * 128u;
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS_QK; ++ks) {
-              const uint32_t koff = (ks >> 2) * 16384 + (ks & 3) * 32;
-              const uint64_t ad = make_sw128_desc(qaddr + s * SM::kTile + koff, 16, 1024);
-              const uint64_t bd = make_sw128_desc(kaddr + st * SM::kTile + koff, 16, 1024);
-              umma_ss(tSs, ad, bd, IDESC_QK, ks > 0 ? 1u : 0u);
-            }
-            umma_commit(&bars->s_full[s]);
-          }
+          prev = cur;
+          pvs[0] = vs[0]; pvs[1] = vs[1]; pvp[0] = vp[0]; pvp[1] = vp[1];
         }
         if (!ok) break;
-        if (prev_bits) umma_commit(&bars->v_empty[prev_st]);
-        if (bits) umma_commit(&bars->k_empty[st]);
-        prev_bits = bits;
-        prev_st = st;
-        prev_j = j;
-      }
-      if (ok) {
-        if (npv[0] > 0) umma_commit(&bars->o_full[0]);
-        if (npv[1] > 0) umma_commit(&bars->o_full[1]);
+        if (rounds > 0) umma_commit(&bars->q_empty);
+        for (int s = 0; s < 2; ++s) {
+          if (npv[s] > 0) {
+            umma_commit(&bars->o_full[s]);
+            ++n_o[s];
+          }
+        }
+        mbar_arrive(&bars->sched_empty[n % kSchedStages]);
       }
       // TMEM must not be freed (nor the CTA retire) while an MMA is still in flight, also on abort.
       umma_commit(&bars->mma_done);
@@ -642,7 +742,74 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     __syncwarp();
   } else {
-    setmaxnreg_dec<kRegsOther>();  // idle warp: only takes part in the register re-balancing
+    // ============================================================ scheduler (warp 11)
+    // Hands out work items from a global counter and builds each item's KV-tile list, one item ahead
+    // of the slowest role.  The counter pair resets itself when the last CTA leaves.
+    setmaxnreg_dec<kRegsOther>();
+    bool ok = true;
+    for (int n = 0; ok; ++n) {
+      const int slot = n % kSchedStages;
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait(&bars->sched_empty[slot], ((n / kSchedStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
+      if (!ok) break;
+      int item = -1;
+      if (lane == 0) {
+        const int idx = atomicAdd(p.sched_counter, 1);
+        if (idx < p.total_items) item = p.work_order ? p.work_order[idx] : idx;
+      }
+      item = __shfl_sync(0xffffffffu, item, 0);
+      int n0 = 0, n1 = 0, aux = 0;
+      if (item >= 0) {
+        const Item im = decode(item);
+        uint16_t* l0 = lists + (slot * 2) * kMaxSteps;
+        uint16_t* l1 = l0 + kMaxSteps;
+        if (MODE == MODE_BLOCK) {
+          const int qb0 = (im.row0[0] >> 7);
+          const uint8_t* m0 = p.mask + im.b * p.m_sb + im.h * p.m_sh + (int64_t)qb0 * p.m_sq;
+          const uint8_t* m1 = m0 + p.m_sq;
+          const uint32_t lt = (1u << lane) - 1u;
+          for (int base = 0; base < p.nkb; base += 32) {
+            const int j = base + lane;
+            const bool on0 = j < p.nkb && (im.live & 1u) && m0[j];
+            const bool on1 = j < p.nkb && (im.live & 2u) && m1[j];
+            const uint32_t v0 = __ballot_sync(0xffffffffu, on0), v1 = __ballot_sync(0xffffffffu, on1);
+            const int p0 = n0 + __popc(v0 & lt), p1 = n1 + __popc(v1 & lt);
+            if (on0 && p0 < kMaxSteps) l0[p0] = (uint16_t)j;
+            if (on1 && p1 < kMaxSteps) l1[p1] = (uint16_t)j;
+            n0 += __popc(v0);
+            n1 += __popc(v1);
+          }
+          n0 = min(n0, kMaxSteps);
+          n1 = min(n1, kMaxSteps);
+        } else {
+          int n = p.nkb;
+          if (MODE == MODE_CSP) {
+            aux = p.counts[im.b * p.c_sb + im.h * p.c_sh + im.group];
+            n = (aux + 127) / 128;
+          }
+          n0 = (im.live & 1u) ? n : 0;
+          n1 = (im.live & 2u) ? n : 0;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        bars->sched[slot].item = item;
+        bars->sched[slot].n0 = n0;
+        bars->sched[slot].n1 = n1;
+        bars->sched[slot].aux = aux;
+        mbar_arrive(&bars->sched_full[slot]);
+      }
+      if (item < 0) break;
+    }
+    if (lane == 0) {
+      __threadfence();
+      if (atomicAdd(p.sched_counter + 1, 1) == (int)gridDim.x - 1) {
+        p.sched_counter[0] = 0;
+        p.sched_counter[1] = 0;
+        __threadfence();
+      }
+    }
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -702,7 +869,6 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
                              a->v_sb, a->v_sh, a->v_sl, a->o_sb, a->o_sh, a->o_sl};
   for (int64_t s : strides)
     LVAR_REQUIRE(s % 8 == 0 && s >= 0, LVAR_ERR_ARG, "tensor strides must be non-negative multiples of 8 elements");
-  LVAR_REQUIRE((int64_t)a->B * a->H <= 65535, LVAR_ERR_UNSUPPORTED, "B*H must be <= 65535");
 
   AttnParams p{};
   p.B = a->B;
@@ -721,7 +887,10 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   p.status = a->dev_status;
   p.wait_limit_ns = a->wait_limit_ns;
 
-  dim3 grid;
+  LVAR_REQUIRE(a->sched_scratch != nullptr, LVAR_ERR_ARG,
+               "sched_scratch must point to two zeroed device int32 (work counter of the persistent kernel)");
+  p.sched_counter = a->sched_scratch;
+  p.work_order = a->work_order;
   if (mode == MODE_BLOCK) {
     LVAR_REQUIRE(a->block_mask != nullptr, LVAR_ERR_ARG, "block mask is null");
     LVAR_REQUIRE(p.nkb <= kMaxSteps, LVAR_ERR_UNSUPPORTED, "Lkv too long for the block list (max %d keys)",
@@ -763,10 +932,17 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     p.oi_sl = a->oi_sl;
     p.o_scale = (float)a->o_scale;
     const int groups = (a->Lq + a->group_rows - 1) / a->group_rows;
-    grid = dim3(groups * p.chunks_per_group, a->B * a->H, 1);
+    p.n_x = groups * p.chunks_per_group;
   } else {
-    grid = dim3((a->Lq + 255) / 256, a->B * a->H, 1);
+    p.n_x = (a->Lq + 255) / 256;
   }
+  const int64_t total = (int64_t)p.n_x * a->B * a->H;
+  LVAR_REQUIRE(total < (1ll << 30), LVAR_ERR_LIMIT, "too many work items");
+  p.total_items = (int)total;
+  int dev = 0, sms = 0;
+  LVAR_CUDA_OK(cudaGetDevice(&dev));
+  LVAR_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
 
   CUtensorMap tq, tk, tv;
   int rc = encode_bhld_map(&tq, a->q, a->B, a->H, a->Lq, a->D, a->q_sb, a->q_sh, a->q_sl, 128);

@@ -44,6 +44,22 @@ def _fill_qkv(a: AttnArgs, q, k, v, o, scale) -> None:
         setattr(a, name + "_sh", t.stride(1))
         setattr(a, name + "_sl", t.stride(2))
     a.wait_limit_ns = _lib.DEFAULT_WAIT_NS
+    a.sched_scratch = _sched_scratch(q.device).data_ptr()
+
+
+_SCRATCH = {}
+
+
+def _sched_scratch(device: torch.device) -> torch.Tensor:
+    """Work counter of the persistent attention kernels: two zeroed int32 per (device, stream).  The
+    kernels leave the counter at zero, so it is allocated and cleared only once."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _SCRATCH.get(key)
+    if buf is None:
+        buf = torch.zeros(2, dtype=torch.int32, device=device)
+        _SCRATCH[key] = buf
+    return buf
 
 
 def new_status(device) -> torch.Tensor:
