@@ -156,6 +156,31 @@ int lvar_mask_to_indices(const uint8_t* mask, int32_t* indices, int32_t* counts,
 int lvar_bitpack(const uint8_t* mask, uint8_t* packed, int64_t n_bits, lvar_stream_t stream);
 int lvar_bitunpack(const uint8_t* packed, uint8_t* mask, int64_t n_bits, lvar_stream_t stream);
 
+/* Largest B*H*Lq the allocation-free entry point below accepts. */
+#define LVAR_STATIC_MAX_ROWS 262144
+
+/* Dense attention plus attention column sums WITHOUT any caller- or library-side allocation:
+ * o = softmax(q k^T * scale) v and cs[b,h,g,j] = sum over the rows of query group g of the softmax
+ * column j (same definitions, layouts and bit patterns as lvar_dense_attn followed by lvar_colsum).
+ * This entry point has no counterpart in the reference; it exists for hosts that cannot call
+ * cudaMalloc on the attention path (all HBM owned by their own pool, or a no-allocation-after-warm-up
+ * rule): the row statistics that connect the two kernels and the attention kernel's work counter
+ * live in a device array that is part of the library image.
+ *   - Limit: B*H*Lq <= LVAR_STATIC_MAX_ROWS, else LVAR_ERR_LIMIT and nothing is launched.  Every GPU
+ *     that loads the library holds that array (2 MiB + 256 B) until the process exits.
+ *   - All calls on a device share the array and it keeps the last call's contents; the call clears
+ *     the one word that must start at zero on `stream`.  Calls that can overlap on the GPU race:
+ *     order them (same stream, or events).
+ *   - The first call on each device resolves the array's address and sets kernel attributes; make it
+ *     before any stream capture.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int lvar_dense_colsum_attn_static(const void* q, const void* k, const void* v, void* o, float* cs, int32_t B,
+                                  int32_t H, int32_t Lq, int32_t Lkv, int32_t D, int64_t q_sb, int64_t q_sh,
+                                  int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl, int64_t v_sb,
+                                  int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh, int64_t o_sl,
+                                  int64_t cs_sb, int64_t cs_sh, int64_t cs_sg, int32_t group_rows, float scale,
+                                  int32_t* dev_status, uint64_t wait_limit_ns, lvar_stream_t stream);
+
 /* Message of the calling thread's most recent failing call ("" if none). Never NULL. */
 const char* lvar_last_error(void);
 

@@ -1,0 +1,78 @@
+"""The allocation-free entry point, lvar_dense_colsum_attn_static, through the C ABI.
+
+Some hosts cannot allocate device memory on the attention path: their own pool owns the whole HBM, or
+they run under a no-allocation-after-warm-up rule where a cudaMalloc per layer is forbidden or would
+stall the device.  For them the library keeps the intermediate row statistics and the attention
+kernel's work counter in a device array of its own.  This test calls that entry point twice in a row
+(the second call reuses the array with the first call's leftovers in it) and compares both results
+with the ordinary entry points lvar_dense_attn + lvar_colsum, which take caller-allocated buffers.
+It is collected last so that a failure here cannot hide any other test under `pytest -x`.
+"""
+import ctypes as C
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+O_MAX, O_MEAN, CS_REL = 2e-2, 2e-3, 1e-3
+MAX_ROWS = 262144  # LVAR_STATIC_MAX_ROWS in include/lvar_b200.h
+
+
+def _call_static(lib, q, k, v, o, cs, group_rows, scale, status):
+    B, H, Lq, D = q.shape
+    return lib.lvar_dense_colsum_attn_static(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), cs.data_ptr(),
+        B, H, Lq, k.shape[2], D,
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+        v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+        cs.stride(0), cs.stride(1), cs.stride(2), group_rows, C.c_float(scale),
+        status.data_ptr(), 2_000_000_000, torch.cuda.current_stream().cuda_stream)
+
+
+def test_static_entry_point_matches_allocating_path_twice():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lvar_b200 import _lib
+    from lvar_b200 import kernels as K
+    lib = _lib.lib
+    g = torch.Generator().manual_seed(2024)
+    # two different problems back to back: the second one finds the first one's statistics in the array
+    for (B, H, Lq, Lkv, D, bm) in [(2, 4, 700, 1300, 128, 256), (1, 3, 333, 900, 64, 192)]:
+        q, k, v = (torch.randn(B, H, n, D, generator=g).bfloat16().cuda() for n in (Lq, Lkv, Lkv))
+        scale = 1.0 / math.sqrt(D)
+        G = (Lq + bm - 1) // bm
+        o = torch.full((B, H, Lq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        cs = torch.full((B, H, G, Lkv), float("nan"), dtype=torch.float32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        rc = _call_static(lib, q, k, v, o, cs, bm, scale, status)
+        assert rc == 0, lib.lvar_last_error().decode()
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+
+        o_ref, M, L = K.dense_attn_fwd(q, k, v, scale)
+        cs_ref = K.colsum_fwd(q, k, M, L, bm, scale)
+        torch.cuda.synchronize()
+        d = (o.float() - o_ref.float()).abs()
+        assert torch.isfinite(o.float()).all() and torch.isfinite(cs).all()
+        assert d.max().item() <= O_MAX and d.mean().item() <= O_MEAN
+        rel = ((cs - cs_ref).abs() / cs_ref.abs().clamp_min(1e-30)).max().item()
+        assert rel <= CS_REL, f"column sums differ: {rel:.3e}"
+
+
+def test_static_entry_point_rejects_oversized_problems():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lvar_b200 import _lib
+    lib = _lib.lib
+    B, H, D, Lkv = 1, 1, 64, 128
+    Lq = MAX_ROWS + 1
+    q = torch.zeros(B, H, Lq, D, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(B, H, Lkv, D, dtype=torch.bfloat16, device="cuda")
+    o = torch.empty_like(q)
+    cs = torch.empty((B, H, (Lq + 255) // 256, Lkv), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = _call_static(lib, q, k, k, o, cs, 256, 0.125, status)
+    assert rc == -4  # LVAR_ERR_LIMIT
+    assert "exceed the static scratch" in lib.lvar_last_error().decode()
