@@ -68,4 +68,45 @@ __device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], uint64_t
 }
 
 
+// exp2 of two values on the FMA pipe (no MUFU): x = j + f with j = round(x), |f| <= 0.5; 2^f by a
+// degree-4 minimax polynomial (relative error 2.7e-6), 2^j by adding j to the exponent field.
+// Valid for -126 <= x <= 100; the caller guarantees the range (no masked, i.e. -inf, inputs).
+__device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& o0, float& o1) {
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);  // 1.5 * 2^23: low mantissa bits = round(x)
+  const uint64_t neg_magic = pack_f32x2(-12582912.f, -12582912.f);
+  const uint64_t t2 = fadd2(x2, magic);
+  const uint64_t j2 = fadd2(t2, neg_magic);
+  const uint64_t f2 = ffma2(j2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t p2 = pack_f32x2(0.00957401655614376f, 0.00957401655614376f);
+  p2 = ffma2(p2, f2, pack_f32x2(0.055918190628290176f, 0.055918190628290176f));
+  p2 = ffma2(p2, f2, pack_f32x2(0.2402464896440506f, 0.2402464896440506f));
+  p2 = ffma2(p2, f2, pack_f32x2(0.6931217312812805f, 0.6931217312812805f));
+  p2 = ffma2(p2, f2, pack_f32x2(0.9999992847442627f, 0.9999992847442627f));
+  float p0, p1, t0, t1;
+  unpack_f32x2(p2, p0, p1);
+  unpack_f32x2(t2, t0, t1);
+  o0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  o1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+// Same as exp_pack_chunk with the exponentials evaluated on the FMA pipe; only for tiles without
+// masked columns.  Inputs below 2^-126 are clamped (they contribute ~1e-38 instead of 0).
+__device__ __forceinline__ void exp_pack_chunk_poly(const uint32_t (&r)[32], uint64_t sc2, uint64_t nm2,
+                                                    uint64_t& sum_a, uint64_t& sum_b, uint32_t (&pk)[32], int off) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
+    const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), sc2, nm2);
+    float a0, a1, b0, b1;
+    unpack_f32x2(t0, a0, a1);
+    unpack_f32x2(t1, b0, b1);
+    exp2_poly_x2(pack_f32x2(fmaxf(a0, -126.f), fmaxf(a1, -126.f)), a0, a1);
+    exp2_poly_x2(pack_f32x2(fmaxf(b0, -126.f), fmaxf(b1, -126.f)), b0, b1);
+    sum_a = fadd2(sum_a, pack_f32x2(a0, a1));
+    sum_b = fadd2(sum_b, pack_f32x2(b0, b1));
+    pk[off + i / 2] = pack_bf16x2(a0, a1);
+    pk[off + i / 2 + 1] = pack_bf16x2(b0, b1);
+  }
+}
+
 }  // namespace lvar

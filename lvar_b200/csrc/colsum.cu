@@ -172,38 +172,55 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       const uint32_t tS = tmem_base + lane_off + (uint32_t)buf * 128u;
       const float4* nc4 = reinterpret_cast<const float4*>(negc + st * 128);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        const int r0 = t * 128 + c * 32;
-        if (r0 >= p.Lq) break;
-        const int g = r0 / p.bm;
+      // the whole S^T row of this thread (128 queries) in registers: one TMEM round trip per tile,
+      // after which the TMEM buffer goes straight back to the MMA warp
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      if (mine) {
+        tmem_ld_x32(tS + 0, r0);
+        tmem_ld_x32(tS + 32, r1);
+        tmem_ld_x32(tS + 64, r2);
+        tmem_ld_x32(tS + 96, r3);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bars->s_empty[buf]);
+      }
+      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      auto chunk = [&](const uint32_t (&r)[32], int c) {
+        const int q0 = t * 128 + c * 32;
+        if (q0 >= p.Lq || !ok) return;
+        const int g = q0 / p.bm;
         if (g != cur_group) {
           ok = flush(cur_group);
           cur_group = g;
-          if (!ok) break;
+          if (!ok) return;
         }
         if (mine) {
-          uint32_t r[32];
-          tmem_ld_x32(tS + c * 32, r);
-          tmem_wait_ld();
-          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+          uint64_t a = 0ull, bsum = 0ull;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float4 nc = nc4[c * 8 + i];
-            a0 += fast_exp2(fmaf(__uint_as_float(r[4 * i + 0]), p.scale_log2, nc.x));
-            a1 += fast_exp2(fmaf(__uint_as_float(r[4 * i + 1]), p.scale_log2, nc.y));
-            a2 += fast_exp2(fmaf(__uint_as_float(r[4 * i + 2]), p.scale_log2, nc.z));
-            a3 += fast_exp2(fmaf(__uint_as_float(r[4 * i + 3]), p.scale_log2, nc.w));
+            const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])), sc2,
+                                      pack_f32x2(nc.x, nc.y));
+            const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), sc2,
+                                      pack_f32x2(nc.z, nc.w));
+            float x0, x1, y0, y1;
+            unpack_f32x2(t0, x0, x1);
+            unpack_f32x2(t1, y0, y1);
+            a = fadd2(a, pack_f32x2(fast_exp2(x0), fast_exp2(x1)));
+            bsum = fadd2(bsum, pack_f32x2(fast_exp2(y0), fast_exp2(y1)));
           }
-          acc += (a0 + a1) + (a2 + a3);
+          float a0, a1, b0, b1;
+          unpack_f32x2(a, a0, a1);
+          unpack_f32x2(bsum, b0, b1);
+          acc += (a0 + a1) + (b0 + b1);
         }
-      }
+      };
+      chunk(r0, 0);
+      chunk(r1, 1);
+      chunk(r2, 2);
+      chunk(r3, 3);
       if (!ok) break;
-      if (mine) {
-        tc_fence_before();
-        mbar_arrive(&bars->s_empty[buf]);
-        mbar_arrive(&bars->q_empty[st]);
-      }
+      if (mine) mbar_arrive(&bars->q_empty[st]);  // the c_i vector of this tile has been read
     }
     if (ok) flush(cur_group);
   } else if (warp == 8) {
