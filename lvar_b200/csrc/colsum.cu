@@ -26,8 +26,9 @@ namespace lvar {
 namespace {
 
 constexpr int kCsThreads = 320;
-constexpr int kQStages = 3;
-constexpr int kSBufs = 4;
+constexpr int kQStages = 2;
+constexpr int kSBufs = 2;
+constexpr uint32_t kCsTmemCols = 256;  // two CTAs per SM: 2 x 256 TMEM columns, 2 x ~100 KB shared memory
 
 struct ColsumParams {
   int B, H, Lq, Lkv, bm, G;
@@ -66,7 +67,7 @@ static_assert(sizeof(CsBars) <= 256, "barrier block too large");
 }  // namespace
 
 template <int D>
-__global__ void __launch_bounds__(kCsThreads, 1)
+__global__ void __launch_bounds__(kCsThreads, 2)
 colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const ColsumParams p) {
   using SM = CsSmem<D>;
@@ -105,7 +106,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     mbar_fence_init();
   }
   if (warp == 9) {
-    tmem_alloc(&bars->tmem_base, 512);
+    tmem_alloc(&bars->tmem_base, kCsTmemCols);
     tmem_relinquish();
   }
   if (warp == 8 && lane == 0) {
@@ -172,20 +173,8 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       const uint32_t tS = tmem_base + lane_off + (uint32_t)buf * 128u;
       const float4* nc4 = reinterpret_cast<const float4*>(negc + st * 128);
-      // the whole S^T row of this thread (128 queries) in registers: one TMEM round trip per tile,
-      // after which the TMEM buffer goes straight back to the MMA warp
-      uint32_t r0[32], r1[32], r2[32], r3[32];
-      if (mine) {
-        tmem_ld_x32(tS + 0, r0);
-        tmem_ld_x32(tS + 32, r1);
-        tmem_ld_x32(tS + 64, r2);
-        tmem_ld_x32(tS + 96, r3);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&bars->s_empty[buf]);
-      }
       const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
-      auto chunk = [&](const uint32_t (&r)[32], int c) {
+      auto chunk = [&](int c) {
         const int q0 = t * 128 + c * 32;
         if (q0 >= p.Lq || !ok) return;
         const int g = q0 / p.bm;
@@ -195,6 +184,9 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (!ok) return;
         }
         if (mine) {
+          uint32_t r[32];
+          tmem_ld_x32(tS + c * 32, r);
+          tmem_wait_ld();
           uint64_t a = 0ull, bsum = 0ull;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -215,12 +207,16 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           acc += (a0 + a1) + (b0 + b1);
         }
       };
-      chunk(r0, 0);
-      chunk(r1, 1);
-      chunk(r2, 2);
-      chunk(r3, 3);
+      chunk(0);
+      chunk(1);
+      chunk(2);
+      chunk(3);
       if (!ok) break;
-      if (mine) mbar_arrive(&bars->q_empty[st]);  // the c_i vector of this tile has been read
+      if (mine) {
+        tc_fence_before();
+        mbar_arrive(&bars->s_empty[buf]);
+        mbar_arrive(&bars->q_empty[st]);  // the c_i vector of this tile has been read
+      }
     }
     if (ok) flush(cur_group);
   } else if (warp == 8) {
@@ -305,7 +301,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   if (warp == 9) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, kCsTmemCols);
   }
 }
 
@@ -314,6 +310,7 @@ static int launch_colsum_d(const CUtensorMap& tq, const CUtensorMap& tk, const C
                            cudaStream_t stream) {
   auto kern = colsum_kernel<D>;
   LVAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem<D>::kDynamic));
+  LVAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
   kern<<<grid, kCsThreads, CsSmem<D>::kDynamic, stream>>>(tq, tk, p);
   LVAR_CUDA_OK(cudaGetLastError());
   return LVAR_OK;
