@@ -320,8 +320,8 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel<128, block-sparse> launch on this
-# workload, from the ncu capture summarised in profiles/ (None until a capture exists).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# workload, from the ncu capture summarised in profiles/ 
+TRAFFIC_BYTES_PER_LAUNCH = 187.5e6  # 165.9 MB read + 21.6 MB written (profiles/attn_fwd_block_sparse_c2.md)
 
 
 def main():
