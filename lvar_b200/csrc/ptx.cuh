@@ -106,7 +106,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA (tiled, no multicast)
+// TMA (tiled loads into this CTA only)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
