@@ -69,7 +69,8 @@ struct AttnParams {
   int64_t oi_sb, oi_sh, oi_sl;
   float o_scale;
   // persistent scheduling
-  int n_x;            // work items per (batch, head)
+  int n_x;            // query-tile pairs per (batch, head)
+  int n_pair_items;   // items [0, n_pair_items) are pairs, [n_pair_items, total_items) single tiles
   int total_items;
   int* sched_counter;  // device int32[2], zero on entry and left zero on exit
   const int32_t* work_order;  // optional permutation of the work items (heaviest first)
@@ -190,8 +191,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int row0[2], row_end[2];
     uint32_t live;  // bit s: slot s has at least one query row
   };
+  // Items below p.n_pair_items are pairs of query tiles; the rest are the single tiles of the last,
+  // partial wave of pairs (see launch_attention), which run with slot 1 idle.
   auto decode = [&](int item) {
     Item it;
+    int half = -1;
+    if (item >= p.n_pair_items) {
+      const int tile = 2 * p.n_pair_items + (item - p.n_pair_items);
+      half = tile & 1;
+      item = tile >> 1;
+    }
     it.bh = item / p.n_x;
     const int x = item % p.n_x;
     it.b = it.bh / p.H;
@@ -208,6 +217,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     it.row0[1] = it.row0[0] + 128;
     it.row_end[0] = it.row_end[1] = gend;
+    if (half >= 0) {  // single tile: slot 0 takes it, slot 1 stays empty
+      it.row0[0] += half * 128;
+      it.row0[1] = gend;
+    }
     it.live = (it.row0[0] < gend ? 1u : 0u) | (it.row0[1] < gend ? 2u : 0u);
     return it;
   };
@@ -878,10 +891,21 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   }
   const int64_t total = (int64_t)p.n_x * a->B * a->H;
   LVAR_REQUIRE(total < (1ll << 30), LVAR_ERR_LIMIT, "too many work items");
-  p.total_items = (int)total;
   int dev = 0, sms = 0;
   LVAR_CUDA_OK(cudaGetDevice(&dev));
   LVAR_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  p.n_pair_items = (int)total;
+  p.total_items = (int)total;
+  if (mode != MODE_CSP && total > sms) {
+    // Wave quantisation: the pairs left over after the last full wave of CTAs are handed out as single
+    // query tiles when those fit in one wave, so that the tail costs one short item per CTA instead of
+    // one full pair on a few CTAs.
+    const int64_t rem = total % sms;
+    if (rem > 0 && 2 * rem <= sms) {
+      p.n_pair_items = (int)(total - rem);
+      p.total_items = (int)(total + rem);
+    }
+  }
   dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
 
   CUtensorMap tq, tk, tv;
