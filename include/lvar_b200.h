@@ -56,10 +56,11 @@ typedef struct lvar_attn_args {
    *   M = max_j(s_ij * scale) * log2(e),  L = sum_j exp2(s_ij * scale * log2e - M)  */
   float* M;
   float* L;
-  /* block-sparse only: uint8 mask [*, *, ceil(Lq/128), ceil(Lkv/128)], nonzero = attend.
+  /* block-sparse only: uint8 mask [*, *, ceil(Lq/bs), ceil(Lkv/bs)], nonzero = attend, bs = block_size.
    * A stride of 0 broadcasts over batch / head. Innermost stride is 1. */
   const uint8_t* block_mask;
   int64_t bm_sb, bm_sh, bm_sq;
+  int32_t block_size; /* 128 (also when 0) or 64 */
   /* column-sparse only */
   const int32_t* indices; /* [B,H,G,>=max count], G = ceil(Lq/group_rows); entries in [0,Lkv) */
   int64_t i_sb, i_sh, i_sg;

@@ -44,6 +44,7 @@ class AttnArgs(C.Structure):
         ("o", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sl", C.c_int64),
         ("M", C.c_void_p), ("L", C.c_void_p),
         ("block_mask", C.c_void_p), ("bm_sb", C.c_int64), ("bm_sh", C.c_int64), ("bm_sq", C.c_int64),
+        ("block_size", C.c_int32),
         ("indices", C.c_void_p), ("i_sb", C.c_int64), ("i_sh", C.c_int64), ("i_sg", C.c_int64),
         ("counts", C.c_void_p), ("c_sb", C.c_int64), ("c_sh", C.c_int64),
         ("group_rows", C.c_int32),

@@ -55,6 +55,8 @@ struct AttnParams {
   const uint8_t* mask;
   int64_t m_sb, m_sh, m_sq;
   int nkb;
+  int mask_block;  // 128, or 64: four mask entries per 128x128 tile (sub-tile bits travel with the list)
+  int nq_mask, nk_mask;  // mask extents in blocks
   // csp (MODE_CSP)
   const int32_t* indices;  // [B,H,G,idx_cols]
   int64_t i_sb, i_sh, i_sg;
@@ -229,8 +231,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     rd.has[0] = r < e.n0;
     rd.has[1] = r < e.n1;
     if (MODE == MODE_BLOCK) {
-      rd.kvb[0] = rd.has[0] ? l0[r] : 0;
-      rd.kvb[1] = rd.has[1] ? l1[r] : 0;
+      rd.kvb[0] = rd.has[0] ? (l0[r] & 0xFFF) : 0;
+      rd.kvb[1] = rd.has[1] ? (l1[r] & 0xFFF) : 0;
     } else {
       rd.kvb[0] = rd.kvb[1] = r;
     }
@@ -276,7 +278,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
       int it = 0;
       for (int j = 0; j < n_mine; ++j) {
-        const int kvb = (MODE == MODE_BLOCK) ? mylist[j] : j;
+        const int kvb = (MODE == MODE_BLOCK) ? (mylist[j] & 0xFFF) : j;
+        const uint32_t sub = (MODE == MODE_BLOCK) ? ((uint32_t)mylist[j] >> 12 >> (2 * (r_in_tile >> 6))) & 3u : 3u;
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, wc, DEV_TIMEOUT_SOFTMAX));
         if (!ok) break;  // warp-uniform: the TMEM accesses below are warp-collective
         ++n_s;
@@ -291,13 +294,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_wait_ld();
 
         const int valid = (MODE == MODE_CSP) ? (cnt_total - j * 128) : (p.Lkv - kvb * 128);
-        if (valid < 128) {
+        if (valid < 128 || sub != 3u) {
+          // columns past the end of K, and (64-wide masks) the column half this row's half does not attend
+          const int lo = (sub & 1u) ? 0 : 64;
+          const int hi = (sub & 2u) ? valid : min(valid, 64);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (i >= valid) s0[i] = 0xff800000u;  // -inf
-            if (i + 32 >= valid) s1[i] = 0xff800000u;
-            if (i + 64 >= valid) s2[i] = 0xff800000u;
-            if (i + 96 >= valid) s3[i] = 0xff800000u;
+            if (i < lo || i >= hi) s0[i] = 0xff800000u;  // -inf
+            if (i + 32 < lo || i + 32 >= hi) s1[i] = 0xff800000u;
+            if (i + 64 < lo || i + 64 >= hi) s2[i] = 0xff800000u;
+            if (i + 96 < lo || i + 96 >= hi) s3[i] = 0xff800000u;
           }
         }
         const float mx = fmax3(fmaxf(chunk_max(s0), chunk_max(s1)), chunk_max(s2), chunk_max(s3));
@@ -332,7 +338,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
         const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
-        const uint64_t nm2 = pack_f32x2(-m_ref, -m_ref);
+        const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;  // row with nothing to attend yet: all p = 0
+        const uint64_t nm2 = pack_f32x2(neg_m, neg_m);
         uint64_t sum_a = 0ull, sum_b = 0ull;  // two packed accumulators = four partial row sums
         {
           uint32_t pk[32];
@@ -366,7 +373,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ++n_o;
         tc_fence_after();
       }
-      const float inv_l = (it > 0) ? (1.0f / l) : 0.f;
+      const float inv_l = (it > 0 && l > 0.f) ? (1.0f / l) : 0.f;
       __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
       const __nv_bfloat16* irow =
           (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
@@ -414,7 +421,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (row_ok && MODE != MODE_CSP) {
         const int64_t si = (int64_t)im.bh * p.Lq + row;
         if (p.M) p.M[si] = m_true;
-        if (p.L) p.L[si] = (it > 0) ? l * fast_exp2(m_ref - m_true) : 0.f;
+        if (p.L) p.L[si] = (it > 0 && l > 0.f) ? l * fast_exp2(m_ref - m_true) : 0.f;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
@@ -717,18 +724,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint16_t* l0 = lists + (slot * 2) * kMaxSteps;
         uint16_t* l1 = l0 + kMaxSteps;
         if (MODE == MODE_BLOCK) {
-          const int qb0 = (im.row0[0] >> 7);
-          const uint8_t* m0 = p.mask + im.b * p.m_sb + im.h * p.m_sh + (int64_t)qb0 * p.m_sq;
-          const uint8_t* m1 = m0 + p.m_sq;
+          // list entry: KV tile (12 bits) | sub-tile bits << 12.  Sub-tile bit (2*rh + ch) is set when the
+          // 64-row half rh of the query tile attends the 64-column half ch of the KV tile; a 128-wide
+          // mask sets all four.
+          const uint8_t* mb = p.mask + im.b * p.m_sb + im.h * p.m_sh;
           const uint32_t lt = (1u << lane) - 1u;
+          auto sub_bits = [&](int qtile, int j) -> uint32_t {
+            if (p.mask_block == 128) return mb[(int64_t)qtile * p.m_sq + j] ? 0xFu : 0u;
+            uint32_t bits = 0;
+#pragma unroll
+            for (int rh = 0; rh < 2; ++rh) {
+              const int qr = 2 * qtile + rh;
+              if (qr >= p.nq_mask) continue;
+              const uint8_t* row = mb + (int64_t)qr * p.m_sq;
+              if (row[2 * j]) bits |= 1u << (2 * rh);
+              if (2 * j + 1 < p.nk_mask && row[2 * j + 1]) bits |= 1u << (2 * rh + 1);
+            }
+            return bits;
+          };
+          const int qt0 = im.row0[0] >> 7, qt1 = im.row0[1] >> 7;
           for (int base = 0; base < p.nkb; base += 32) {
             const int j = base + lane;
-            const bool on0 = j < p.nkb && (im.live & 1u) && m0[j];
-            const bool on1 = j < p.nkb && (im.live & 2u) && m1[j];
-            const uint32_t v0 = __ballot_sync(0xffffffffu, on0), v1 = __ballot_sync(0xffffffffu, on1);
+            const uint32_t b0 = (j < p.nkb && (im.live & 1u)) ? sub_bits(qt0, j) : 0u;
+            const uint32_t b1 = (j < p.nkb && (im.live & 2u)) ? sub_bits(qt1, j) : 0u;
+            const uint32_t v0 = __ballot_sync(0xffffffffu, b0 != 0), v1 = __ballot_sync(0xffffffffu, b1 != 0);
             const int p0 = n0 + __popc(v0 & lt), p1 = n1 + __popc(v1 & lt);
-            if (on0 && p0 < kMaxSteps) l0[p0] = (uint16_t)j;
-            if (on1 && p1 < kMaxSteps) l1[p1] = (uint16_t)j;
+            if (b0 && p0 < kMaxSteps) l0[p0] = (uint16_t)(j | (b0 << 12));
+            if (b1 && p1 < kMaxSteps) l1[p1] = (uint16_t)(j | (b1 << 12));
             n0 += __popc(v0);
             n1 += __popc(v1);
           }
@@ -846,8 +868,13 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   p.work_order = a->work_order;
   if (mode == MODE_BLOCK) {
     LVAR_REQUIRE(a->block_mask != nullptr, LVAR_ERR_ARG, "block mask is null");
-    LVAR_REQUIRE(p.nkb <= kMaxSteps, LVAR_ERR_UNSUPPORTED, "Lkv too long for the block list (max %d keys)",
+    LVAR_REQUIRE(p.nkb <= kMaxSteps && p.nkb <= 4096, LVAR_ERR_UNSUPPORTED, "Lkv too long for the block list (max %d keys)",
                  kMaxSteps * 128);
+    LVAR_REQUIRE(a->block_size == 0 || a->block_size == 128 || a->block_size == 64, LVAR_ERR_ARG,
+                 "block_size must be 128 or 64");
+    p.mask_block = a->block_size == 64 ? 64 : 128;
+    p.nq_mask = (a->Lq + p.mask_block - 1) / p.mask_block;
+    p.nk_mask = (a->Lkv + p.mask_block - 1) / p.mask_block;
     p.mask = a->block_mask;
     p.m_sb = a->bm_sb;
     p.m_sh = a->bm_sh;

@@ -94,13 +94,15 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
     return o, M, L
 
 
-def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None):
-    """Attention under a 128x128 block mask (uint8/bool, shape [nq,nk], [H,nq,nk] or [B,H,nq,nk])."""
+def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None, block=128):
+    """Attention under a block mask of 128x128 (or 64x64) blocks: uint8/bool [nq,nk], [H,nq,nk] or [B,H,nq,nk]."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
     B, H, Lq, _ = q.shape
     Lkv = k.shape[2]
-    nq, nk = (Lq + 127) // 128, (Lkv + 127) // 128
+    if block not in (64, 128):
+        raise RuntimeError("block must be 128 or 64")
+    nq, nk = (Lq + block - 1) // block, (Lkv + block - 1) // block
     m = block_mask
     if m.dtype == torch.bool:
         m = m.view(torch.uint8)
@@ -120,6 +122,7 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
     a.bm_sb = m.stride(0) if m.shape[0] > 1 else 0
     a.bm_sh = m.stride(1) if m.shape[1] > 1 else 0
     a.bm_sq = m.stride(2)
+    a.block_size = int(block)
     M = L = None
     if return_stats:
         M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)

@@ -87,11 +87,11 @@ def csp_attn(q, k, v, scale, indices, indices_counts, o, o_scale):
     return K.csp_attn_fwd(q, k, v, indices, indices_counts, o, int(o_scale), bm, scale)
 
 
-def block_sparse_attn(q, k, v, block_mask, scale=None):
-    """Attention under a 128x128 block mask ([nq,nk], [H,nq,nk] or [B,H,nq,nk], bool); the kernel
+def block_sparse_attn(q, k, v, block_mask, scale=None, block_size=128):
+    """Attention under a block mask of 128x128 (or 64x64) blocks ([nq,nk], [H,nq,nk] or [B,H,nq,nk], bool); the kernel
     behind ``SparseFlexAttn.forward`` in this package, standing in for
     ``flex_attention(q, k, v, block_mask=...)`` (models/sparvar/basic_sparvar.py:187-194)."""
-    return K.block_sparse_attn_fwd(q, k, v, block_mask, scale)
+    return K.block_sparse_attn_fwd(q, k, v, block_mask, scale, block=block_size)
 
 
 def bitpack(mask: torch.Tensor):

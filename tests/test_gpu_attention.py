@@ -140,6 +140,50 @@ def test_block_sparse_matches_oracle(K):
     _check_o(o, oa.block_sparse_attn(q, k, v, bm))
 
 
+def test_block_sparse_64_wide_blocks(K):
+    """64x64 block masks: four mask entries per 128x128 MMA tile, including row halves with nothing to attend."""
+    from oracle import attention as oa
+    for (B, H, Lq, Lkv, D, dens, seed) in [(1, 2, 200, 500, 64, 0.4, 21), (2, 2, 700, 1500, 128, 0.3, 22)]:
+        q, k, v = _qkv(B, H, Lq, Lkv, D, seed=seed)
+        nq, nk = (Lq + 63) // 64, (Lkv + 63) // 64
+        g = torch.Generator().manual_seed(seed)
+        bm = torch.rand(B, H, nq, nk, generator=g) < dens
+        bm[..., 0] = True
+        bm[0, 0, 1] = False  # a 64-row half with no block at all -> zeros
+        st = K.new_status("cuda")
+        o, M, L = K.block_sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), bm.cuda(), status=st, block=64,
+                                          return_stats=True)
+        _ok_status(K, st)
+        _check_o(o, oa.block_sparse_attn(q, k, v, bm, block=64))
+        assert o[0, 0, 64:128].abs().max().item() == 0.0
+        assert (L[0, 0, 64:128] == 0).all()
+
+
+def test_var_d16_config_end_to_end(K):
+    """VAR-d16 shape (B2 H16 D64, last scale 16x16 against all 10 scales, Lkv 680): column sums -> 64x64
+    block scores -> mask (scales <= 8x8, own position, top 25 % of the rest) -> block-sparse attention."""
+    from lvar_b200 import policy as P
+    from oracle import attention as oa
+    from oracle import indexing as oi
+    B, H, Lq, Lkv, D, blk = 2, 16, 256, 680, 64, 64
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=0)
+    scale = 1.0 / 8.0
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o_d, M, L = K.dense_attn_fwd(qc, kc, vc, scale)
+    cs = K.colsum_fwd(qc, kc, M, L, blk, scale)
+    _, cs_ref = oa.dense_colsum_attn(q, k, v, scale, q_group_size=blk, dtype=torch.float64)
+    assert ((cs.double().cpu() - cs_ref).abs() / cs_ref).max().item() <= CS_REL
+    nq, nk = 4, 11
+    always = P.sink_local_blocks(nq, nk, blk, 155, 424, 0, Lq)
+    assert torch.equal(always, oi.sink_local_blocks(nq, nk, blk, 155, 424, 0, Lq))
+    k_total = int(always[0].sum()) + math.ceil(0.25 * int((~always[0]).sum()))
+    scores = K.block_scores(cs, blk)
+    mask = K.build_block_mask(scores, always.cuda(), k_total)
+    assert torch.equal(mask.cpu(), oi.build_block_mask(scores.cpu(), always, k_total))  # identical score inputs
+    o = K.block_sparse_attn_fwd(qc, kc, vc, mask, scale, block=blk)
+    _check_o(o, oa.block_sparse_attn(q, k, v, mask.cpu(), scale, block=blk))
+
+
 def test_block_sparse_csla_mask_last_scale(K):
     """Static sink + local-window block mask of the last Infinity scale (Lq 4096, Lkv 10521), one head."""
     from lvar_b200 import policy as P
