@@ -304,8 +304,8 @@ class SparseFlexAttn:
 
     def __init__(self, scale_schedule, kernel_schedule, q_scale_idx, attn_sink_scale, block_size: int = 128,
                  num_heads: int = 16, device="cuda"):
-        if block_size != 128:
-            raise ValueError("the block-sparse kernel works on 128x128 blocks")
+        if block_size not in (64, 128):
+            raise ValueError("the block-sparse kernel works on 128x128 or 64x64 blocks")
         self.block_size = block_size
         self.block_mask_cpu = csla_block_mask(scale_schedule, kernel_schedule, q_scale_idx, attn_sink_scale, block_size)
         self.block_mask = self.block_mask_cpu.to(device) if torch.cuda.is_available() else None
@@ -314,6 +314,6 @@ class SparseFlexAttn:
         from .sparse_attn_ops import block_sparse_attn
         if self.block_mask is None or self.block_mask.device != q.device:
             self.block_mask = self.block_mask_cpu.to(q.device)
-        return block_sparse_attn(q.to(v.dtype), k.to(v.dtype), v, self.block_mask, scale)
+        return block_sparse_attn(q.to(v.dtype), k.to(v.dtype), v, self.block_mask, scale, self.block_size)
 
     __call__ = forward

@@ -1,0 +1,97 @@
+"""The larger benchmark configurations on the GPU: ScaleKV-style per-scale scoring + top-k over the
+13-scale 1024^2 schedule, and the 2048^2-style last scale with a +-2 block window + top-k mask.
+Full-size results are checked with size-independent properties and with PyTorch attention on the GPU as
+the checker for sampled heads; index selections are compared bit for bit with the CPU oracle fed with
+the same scores."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SCALES = [1, 2, 4, 6, 8, 12, 16, 20, 24, 32, 40, 48, 64]
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lvar_b200 import kernels
+    return kernels
+
+
+def _peaked_qkv(B, H, Lq, Lkv, D, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(B, H, Lq, D, generator=g, device="cuda")
+    k = torch.randn(B, H, Lkv, D, generator=g, device="cuda")
+    v = torch.randn(B, H, Lkv, D, generator=g, device="cuda")
+    k = k + 2.0 * (torch.randn(B, H, Lkv, 8, generator=g, device="cuda") @ torch.randn(B, H, 8, D, generator=g, device="cuda"))
+    return q.bfloat16(), k.bfloat16(), v.bfloat16()
+
+
+def test_per_scale_colsum_and_token_topk(K):
+    """Every scale's queries scored against the cumulative KV, one column-sum row per head, 10 % of the
+    KV tokens kept per head, indices ascending."""
+    from oracle import indexing as oi
+    B, H, D = 2, 16, 128
+    cum = [0]
+    for s in SCALES:
+        cum.append(cum[-1] + s * s)
+    expect_k = [0, 0, 2, 6, 12, 26, 52, 92, 150, 252, 412, 642, 1052]
+    q_all, k_all, v_all = _peaked_qkv(B, H, cum[-1], cum[-1], D, seed=3)
+    scale = 1.0 / math.sqrt(D)
+    for si, s in enumerate(SCALES):
+        Lq, Lkv = s * s, cum[si + 1]
+        q = q_all[:, :, cum[si]:cum[si + 1]].contiguous()
+        k, v = k_all[:, :, :Lkv], v_all[:, :, :Lkv]
+        group = (Lq + 31) // 32 * 32
+        o, M, L = K.dense_attn_fwd(q, k, v, scale)
+        cs = K.colsum_fwd(q, k, M, L, group, scale)
+        assert cs.shape == (B, H, 1, Lkv)
+        assert torch.allclose(cs.sum(-1), torch.full((B, H, 1), float(Lq), device="cuda"), rtol=1e-3)
+        if Lkv <= 2521:  # direct check against PyTorch on the GPU for the small scales
+            p = torch.softmax((q.float() @ k.float().transpose(-1, -2)) * scale, dim=-1).sum(2, keepdim=True)
+            assert ((cs - p).abs() / p).max().item() <= 1e-3
+        keep = round(0.1 * Lkv)
+        assert keep == expect_k[si]
+        sel = K.topk_indices(cs, keep, ascending_index=True)
+        assert sel.shape == (B, H, 1, keep)
+        assert torch.equal(sel.cpu(), oi.topk_indices(cs.cpu(), keep, ascending_index=True))
+        if keep > 1:
+            assert (sel[..., 1:] > sel[..., :-1]).all()
+
+
+def test_2048px_style_last_scale_window_plus_topk(K):
+    """Lq 16384, Lkv 24576, 128x128 blocks at ~10 %: window of +-2 blocks around the diagonal plus top-k
+    to 19 blocks per row; the per-GPU slice of the 8-way head shard (2 batch x 4 heads)."""
+    from lvar_b200 import policy as P
+    from oracle import indexing as oi
+    B, H, Lq, Lkv, D = 2, 4, 16384, 24576, 128
+    q, k, v = _peaked_qkv(B, H, Lq, Lkv, D, seed=4)
+    scale = 1.0 / math.sqrt(D)
+    st = K.new_status("cuda")
+    o_d, M, L = K.dense_attn_fwd(q, k, v, scale, status=st)
+    cs = K.colsum_fwd(q, k, M, L, 128, scale, status=st)
+    scores = K.block_scores(cs, 128)
+    nq, nk = 128, 192
+    always = P.sink_local_blocks(nq, nk, 128, 0, Lkv - Lq, 2, Lq)
+    assert int(always.sum(-1).max()) == 5
+    mask = K.build_block_mask(scores, always.cuda(), 19)
+    assert (mask.sum(-1) == 19).all()
+    sample = [(0, 0), (1, 3)]
+    for b, h in sample:
+        ref = oi.build_block_mask(scores[b:b + 1, h:h + 1].cpu(), always, 19)
+        assert torch.equal(mask[b:b + 1, h:h + 1].cpu(), ref)
+    o = K.block_sparse_attn_fwd(q, k, v, mask, scale, status=st)
+    assert K.read_status(st)[0] == 0
+    for b, h in sample:
+        rows = slice(5000, 5000 + 1024)
+        fine = mask[b, h].repeat_interleave(128, 0)[rows].repeat_interleave(128, 1)
+        s = (q[b, h, rows].float() @ k[b, h].float().T) * scale
+        ref = torch.softmax(s.masked_fill(~fine, float("-inf")), dim=-1) @ v[b, h].float()
+        d = (o[b, h, rows].float() - ref).abs()
+        assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
+    # keeping every block reproduces dense attention bit for bit
+    ones = torch.ones(nq, nk, dtype=torch.bool, device="cuda")
+    assert torch.equal(K.block_sparse_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], ones, scale), o_d[:1, :1])
