@@ -157,6 +157,27 @@ int lvar_mask_to_indices(const uint8_t* mask, int32_t* indices, int32_t* counts,
 int lvar_bitpack(const uint8_t* mask, uint8_t* packed, int64_t n_bits, lvar_stream_t stream);
 int lvar_bitunpack(const uint8_t* packed, uint8_t* mask, int64_t n_bits, lvar_stream_t stream);
 
+/* Key lists of a sparse step from the decision-scale lists: for each target query group g the list of
+ * source group remap[g] (first cnt entries, clamped to [0, k_len); a source list shorter than cnt is
+ * stretched by repeating each entry), then the scale's static local band band[g, 0:band_count];
+ * out int32 [BH, Gk, out_cols] (tail 0), counts int32 [BH, Gk] = count_value (the reference writes
+ * the unrounded source count + band_count there, cnt being that source count rounded up to the list padding).
+ * src int32 [BH, Gs, >= src_cols] with the given strides; remap int32 [Gk]; band int32 [Gk, band_count].
+ * One pass on the device instead of the reference's index_select / repeat_interleave / clamp / two
+ * torch.cat with a host read of the count (models/sparvar/sparse_attn.py:365-421 and 1056-1121). */
+int lvar_sparse_step_lists(const int32_t* src, const int32_t* remap, const int32_t* band, int32_t* out,
+                           int32_t* counts, int64_t BH, int32_t Gs, int32_t src_cols, int64_t src_g_stride,
+                           int64_t src_bh_stride, int32_t Gk, int32_t cnt, int32_t band_count, int32_t k_len,
+                           int32_t out_cols, int32_t count_value, lvar_stream_t stream);
+
+/* Bilinear (align_corners = false) resize of an attention-output cache between two square token grids:
+ * src bf16 [BH, src_side^2, D] -> dst bf16 [BH, dst_side^2, D] (strides in elements, D a multiple of 8).
+ * Replaces upsample_Ocache(o, L_src, L_tgt, mode='2d', upsample_mode='bilinear')
+ * (models/sparvar/sparse_attn.py:324-362), which reshapes and calls F.interpolate. */
+int lvar_upsample_ocache(const void* src, void* dst, int64_t BH, int32_t src_side, int32_t dst_side, int32_t D,
+                         int64_t src_bh_stride, int64_t src_row_stride, int64_t dst_bh_stride,
+                         int64_t dst_row_stride, lvar_stream_t stream);
+
 /* Largest B*H*Lq the allocation-free entry point below accepts. */
 #define LVAR_STATIC_MAX_ROWS 262144
 

@@ -72,6 +72,10 @@ _SIGNATURES = {
     "lvar_bitunpack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lvar_dense_colsum_attn_static": (C.c_int, [C.c_void_p] * 5 + [C.c_int32] * 5 + [C.c_int64] * 15 +
                                       [C.c_int32, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "lvar_sparse_step_lists": (C.c_int, [C.c_void_p] * 5 + [C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int64] +
+                               [C.c_int32] * 6 + [C.c_void_p]),
+    "lvar_upsample_ocache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32] +
+                             [C.c_int64] * 4 + [C.c_void_p]),
     "lvar_last_error": (C.c_char_p, []),
     "lvar_version": (C.c_char_p, []),
     "lvar_kernel_config_attn": (None, [C.POINTER(C.c_int32)] * 3),

@@ -80,9 +80,32 @@ int launch_mask_to_indices(const uint8_t* mask, int32_t* indices, int32_t* count
 int launch_bitpack(const uint8_t* mask, uint8_t* packed, int64_t n_bits, cudaStream_t stream);
 int launch_bitunpack(const uint8_t* packed, uint8_t* mask, int64_t n_bits, cudaStream_t stream);
 
+int launch_sparse_step_lists(const int32_t* src, const int32_t* remap, const int32_t* band, int32_t* out,
+                             int32_t* counts, int64_t BH, int Gs, int src_cols, int64_t src_g_stride,
+                             int64_t src_bh_stride, int Gk, int cnt, int band_count, int k_len, int out_cols,
+                             int count_value, cudaStream_t stream);
+int launch_upsample_ocache(const void* src, void* dst, int64_t BH, int src_side, int dst_side, int D,
+                           int64_t src_bh_stride, int64_t src_row_stride, int64_t dst_bh_stride,
+                           int64_t dst_row_stride, cudaStream_t stream);
+
 }  // namespace lvar
 
 extern "C" {
+
+int lvar_sparse_step_lists(const int32_t* src, const int32_t* remap, const int32_t* band, int32_t* out,
+                           int32_t* counts, int64_t BH, int32_t Gs, int32_t src_cols, int64_t src_g_stride,
+                           int64_t src_bh_stride, int32_t Gk, int32_t cnt, int32_t band_count, int32_t k_len,
+                           int32_t out_cols, int32_t count_value, lvar_stream_t stream) {
+  return lvar::launch_sparse_step_lists(src, remap, band, out, counts, BH, Gs, src_cols, src_g_stride, src_bh_stride,
+                                        Gk, cnt, band_count, k_len, out_cols, count_value, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_upsample_ocache(const void* src, void* dst, int64_t BH, int32_t src_side, int32_t dst_side, int32_t D,
+                         int64_t src_bh_stride, int64_t src_row_stride, int64_t dst_bh_stride,
+                         int64_t dst_row_stride, lvar_stream_t stream) {
+  return lvar::launch_upsample_ocache(src, dst, BH, src_side, dst_side, D, src_bh_stride, src_row_stride,
+                                      dst_bh_stride, dst_row_stride, static_cast<cudaStream_t>(stream));
+}
 
 int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream) {
   return lvar::launch_attention(args, 0, static_cast<cudaStream_t>(stream));

@@ -296,7 +296,56 @@ __global__ void bitunpack_kernel(const uint8_t* __restrict__ packed, uint8_t* __
   mask[i] = (packed[i >> 3] >> (i & 7)) & 1u;
 }
 
+// ------------------------------------------------------------------------------------------------
+// index lists of a sparse step: remapped decision-scale lists followed by the scale's local band
+// ------------------------------------------------------------------------------------------------
+// out[bh, g, c] = clamp(src[bh, remap[g], c / rep], 0, k_len - 1)   for c <  cnt
+//               = band[g, c - cnt]                                  for cnt <= c < cnt + band_count
+//               = 0                                                 beyond;   counts[bh, g] = count_value
+__global__ void sparse_step_lists_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ remap,
+                                         const int32_t* __restrict__ band, int32_t* __restrict__ out,
+                                         int32_t* __restrict__ counts, int64_t BH, int Gs, int64_t src_g_stride,
+                                         int64_t src_bh_stride, int Gk, int cnt, int rep, int band_count, int k_len,
+                                         int out_cols, int count_value) {
+  const int64_t total = BH * Gk * out_cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % out_cols);
+    const int g = (int)((i / out_cols) % Gk);
+    const int64_t bh = i / ((int64_t)out_cols * Gk);
+    int32_t v = 0;
+    if (c < cnt) {
+      v = src[bh * src_bh_stride + (int64_t)remap[g] * src_g_stride + c / rep];
+      v = max(0, min(v, k_len - 1));
+    } else if (c < cnt + band_count) {
+      v = band[(int64_t)g * band_count + (c - cnt)];
+    }
+    out[i] = v;
+    if (c == 0) counts[bh * Gk + g] = count_value;
+  }
+}
+
 }  // namespace
+
+int launch_sparse_step_lists(const int32_t* src, const int32_t* remap, const int32_t* band, int32_t* out,
+                             int32_t* counts, int64_t BH, int Gs, int src_cols, int64_t src_g_stride,
+                             int64_t src_bh_stride, int Gk, int cnt, int band_count, int k_len, int out_cols,
+                             int count_value, cudaStream_t stream) {
+  LVAR_REQUIRE(src && remap && out && counts, LVAR_ERR_ARG, "src, remap, out and counts must be non-null");
+  LVAR_REQUIRE(band != nullptr || band_count == 0, LVAR_ERR_ARG, "band is null but band_count > 0");
+  LVAR_REQUIRE(BH >= 1 && Gs >= 1 && Gk >= 1 && src_cols >= 1 && k_len >= 1, LVAR_ERR_ARG, "bad sizes");
+  LVAR_REQUIRE(cnt >= 0 && band_count >= 0 && cnt + band_count <= out_cols, LVAR_ERR_ARG,
+               "cnt + band_count = %d does not fit in %d output columns", cnt + band_count, out_cols);
+  // lists shorter than cnt are stretched by repeating every entry `rep` times (repeat_interleave)
+  const int rep = src_cols >= cnt ? 1 : (cnt + src_cols - 1) / src_cols;
+  const int64_t total = BH * Gk * out_cols;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  sparse_step_lists_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src, remap, band, out, counts, BH, Gs, src_g_stride,
+                                                                 src_bh_stride, Gk, cnt, rep, band_count, k_len,
+                                                                 out_cols, count_value);
+  LVAR_CUDA_OK(cudaGetLastError());
+  return LVAR_OK;
+}
 
 int launch_block_scores(const float* cs, float* out, int64_t rows, int Lkv, int block, int64_t cs_row_stride,
                         cudaStream_t stream) {

@@ -288,3 +288,45 @@ def bitunpack(packed: torch.Tensor, original_shape):
     out = torch.empty((total,), dtype=torch.uint8, device=packed.device)
     check(lib.lvar_bitunpack(packed.contiguous().data_ptr(), out.data_ptr(), total, _stream_ptr(packed.device)))
     return out.view(torch.bool).view(*original_shape)
+
+
+def upsample_ocache(o_cache: torch.Tensor, L_src: int, L_tgt: int) -> torch.Tensor:
+    """Bilinear resize of a bf16 output cache [B,H,L_src,D] (square token grid) to [B,H,L_tgt,D]."""
+    _require_cuda_bf16("o_cache", o_cache)
+    B, H, L, D = o_cache.shape
+    s, t = int(round(L_src ** 0.5)), int(round(L_tgt ** 0.5))
+    _require(L == L_src and s * s == L_src and t * t == L_tgt, "L_src and L_tgt must be square token counts")
+    src = o_cache if o_cache.is_contiguous() else o_cache.contiguous()
+    dst = torch.empty((B, H, L_tgt, D), dtype=torch.bfloat16, device=o_cache.device)
+    check(lib.lvar_upsample_ocache(src.data_ptr(), dst.data_ptr(), B * H, s, t, D, src.stride(1), src.stride(2),
+                                   dst.stride(1), dst.stride(2), _stream_ptr(o_cache.device)))
+    return dst
+
+
+def sparse_step_lists(inds: torch.Tensor, remap: torch.Tensor, band: Optional[torch.Tensor], cnt: int, k_len: int,
+                      *, src_cols: Optional[int] = None, count_value: Optional[int] = None):
+    """Key lists of a sparse step: inds int32 [B,H,Gs,*] remapped to the groups in `remap` (int32 [Gk]),
+    first `cnt` entries clamped to [0, k_len), followed by band int32 [Gk, band_count]; returns
+    (lists int32 [B,H,Gk,k_len], counts int32 [B,H,Gk])."""
+    _require(inds.is_cuda and inds.dtype == torch.int32 and inds.dim() == 4 and inds.stride(-1) == 1,
+             "inds must be a CUDA int32 [B,H,Gs,cols] tensor with a contiguous last dimension")
+    _require(remap.is_cuda and remap.dtype == torch.int32 and remap.dim() == 1, "remap must be CUDA int32 [Gk]")
+    B, H, Gs, cols = inds.shape
+    if inds.stride(0) != H * inds.stride(1):
+        inds = inds.contiguous()
+    Gk = remap.shape[0]
+    band_count = 0
+    if band is not None:
+        _require(band.is_cuda and band.dtype == torch.int32 and band.dim() == 2 and band.shape[0] == Gk,
+                 "band must be CUDA int32 [Gk, band_count]")
+        band = band.contiguous()
+        band_count = band.shape[1]
+    out = torch.empty((B, H, Gk, k_len), dtype=torch.int32, device=inds.device)
+    counts = torch.empty((B, H, Gk), dtype=torch.int32, device=inds.device)
+    check(lib.lvar_sparse_step_lists(inds.data_ptr(), remap.data_ptr(), band.data_ptr() if band is not None else None,
+                                     out.data_ptr(), counts.data_ptr(), B * H, Gs,
+                                     int(cols if src_cols is None else src_cols), inds.stride(2), inds.stride(1),
+                                     Gk, int(cnt), band_count, int(k_len), k_len,
+                                     int(cnt + band_count if count_value is None else count_value),
+                                     _stream_ptr(inds.device)))
+    return out, counts

@@ -220,7 +220,7 @@ class SparseDiffAttn:
             s = spsd_scale + 1 + i
             band, count = local_band(self.scales, s, wind_size[i], self.bm, self.multiple_of)
             self.local_inds[s] = (band.to(torch.int32), count)
-        self._device_cache: Dict[Tuple[int, str], torch.Tensor] = {}
+        self._device_cache: Dict[tuple, torch.Tensor] = {}
         self.speedup = speedup
 
     # -- helpers ----------------------------------------------------------------------------------
@@ -230,6 +230,12 @@ class SparseDiffAttn:
         if key not in self._device_cache:
             self._device_cache[key] = band.to(device)
         return self._device_cache[key], count
+
+    def _remap_on(self, Gk: int, Gs: int, device) -> torch.Tensor:
+        key = (Gk, Gs, str(device))
+        if key not in self._device_cache:
+            self._device_cache[key] = group_remap_table(Gk, Gs).to(device=device, dtype=torch.int32)
+        return self._device_cache[key]
 
     def _pad_lists(self, inds: torch.Tensor, k_len: int) -> torch.Tensor:
         """Pads the list dimension to k_len columns (zeros where the reference leaves torch.empty)."""
@@ -259,23 +265,16 @@ class SparseDiffAttn:
         inds, s_count = st.indices[:B], st.count_value
         Gk, Gs = (q_len + self.bm - 1) // self.bm, inds.shape[2]
         cnt = max(self.indices_pad_to, (s_count + self.indices_pad_to - 1) // self.indices_pad_to * self.indices_pad_to)
-        remap = group_remap_table(Gk, Gs).to(inds.device)
-        templ = inds.index_select(2, remap)
-        if templ.shape[-1] >= cnt:
-            templ = templ[..., :cnt]
-        else:
-            templ = templ.repeat_interleave(math.ceil(cnt / templ.shape[-1]), dim=-1)[..., :cnt]
-        templ = templ.clamp(0, max(0, k_len - 1))
         band, band_count = self._band_on(scale_ind, inds.device)
         total = s_count + band_count
         assert total % self.multiple_of == 0, f"after add local sparse index, mismatch multiple_of={self.multiple_of}"
-        lists = self._pad_lists(torch.cat([templ, band.expand(B, H, -1, -1)], dim=-1), k_len)
-        counts = torch.full((B, H, Gk), total, dtype=torch.int32, device=q.device)
+        lists, counts = K.sparse_step_lists(inds, self._remap_on(Gk, Gs, inds.device), band, cnt, k_len,
+                                            count_value=total)
         if scale_ind != len(self.scales) - 1:
             st.indices, st.counts, st.count_value = lists, counts, total
         if self.use_o_cache:
             cache = st.out_cache[:B]
-            o = upsample_ocache(cache, cache.shape[-2], q_len).to(v.dtype)
+            o = K.upsample_ocache(cache.to(v.dtype), cache.shape[-2], q_len)
         else:
             o = torch.zeros_like(q)
         return csp_attn(q, k, v, scale, lists, counts, o, 1)

@@ -111,3 +111,44 @@ def test_bitpack_roundtrip_and_layout(K):
         packed, shp = K.bitpack(m.cuda())
         assert torch.equal(packed.cpu(), oi.bitpack(m)[0])
         assert torch.equal(K.bitunpack(packed, shp).cpu(), m)
+
+
+def test_upsample_ocache_matches_interpolate(K, golden_indices):
+    """Bilinear O-cache resize against F.interpolate (what the reference calls) and its golden output."""
+    from oracle import indexing as oi
+    g = golden_indices
+    got = K.upsample_ocache(g["upsample_in"].bfloat16().cuda(), 36, 64)
+    ref = oi.upsample_ocache(g["upsample_in"].bfloat16().float(), 36, 64)
+    assert (got.float().cpu() - ref).abs().max().item() <= 2e-2
+    gen = torch.Generator().manual_seed(3)
+    for (B, H, s, t, D) in ((2, 3, 40, 48, 128), (1, 2, 48, 64, 128), (1, 1, 5, 16, 64), (1, 2, 8, 8, 64)):
+        x = torch.randn(B, H, s * s, D, generator=gen).bfloat16()
+        got = K.upsample_ocache(x.cuda(), s * s, t * t).cpu()
+        ref = oi.upsample_ocache(x.float(), s * s, t * t)
+        assert got.shape == (B, H, t * t, D)
+        d = (got.float() - ref).abs()
+        # fp32 interpolation of bf16 inputs, one bf16 rounding of the result
+        assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("src_cols,s_count", [(1521, 384), (96, 256), (640, 130)])
+def test_sparse_step_lists_match_oracle(K, src_cols, s_count):
+    """Remap + stretch + clamp + band append in one kernel, bit-exact against the CPU restatement."""
+    from oracle import indexing as oi
+    from lvar_b200 import policy as P
+    torch.manual_seed(5)
+    B, H, Gs, bm, mult, pad_to = 2, 3, 5, 256, 2, 4
+    q_len, k_len = 9 * 256 - 17, 4000
+    Gk = (q_len + bm - 1) // bm
+    inds = torch.randint(0, 5000, (B, H, Gs, src_cols), dtype=torch.int32)
+    counts = torch.full((B, H, Gs), s_count, dtype=torch.int32)
+    band_count = 70
+    band = (torch.arange(band_count)[None, :] + torch.arange(Gk)[:, None] * 11).to(torch.int32)
+    want, want_counts = oi.sparse_step_indices(inds, counts, q_len, k_len, band, band_count, bm, mult, pad_to)
+    cnt = max(pad_to, (s_count + pad_to - 1) // pad_to * pad_to)
+    remap = P.group_remap_table(Gk, Gs).to(device="cuda", dtype=torch.int32)
+    got, got_counts = K.sparse_step_lists(inds.cuda(), remap, band.cuda(), cnt, k_len,
+                                          count_value=s_count + band_count)
+    assert torch.equal(got.cpu(), want)
+    assert torch.equal(got_counts.cpu(), want_counts)
