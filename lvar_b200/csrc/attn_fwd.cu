@@ -9,15 +9,16 @@
 //   warps 4-7   softmax warpgroup of slot 1
 //   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp
 //   warp  9     V loader
-//   warp  10    allocates TMEM and issues every tcgen05.mma from one thread
-//   warp  11    idle; completes the fourth warpgroup so registers can be re-balanced (setmaxnreg)
+//   warp  10    allocates TMEM; lane 0 issues every tcgen05.mma (descriptor words precomputed, all lanes
+//               run the bookkeeping so that it stays out of a divergent branch)
+//   warp  11    scheduler: takes work items from the global counter and builds their KV-tile lists
 // TMEM (512 columns x 128 lanes, fp32): S0 | S1 | O0 | O1.  S_s = Q_s K^T lands in S_s; the softmax
 // warpgroup overwrites the first 64 columns of S_s with bf16 P_s, which is then the TMEM A operand of
 // O_s += P_s V.  Shared memory: Q0,Q1 + 2 K stages + 2 V stages, all 128-byte-swizzled [128][64]
 // bf16 sub-tiles (exactly what a [64 x 128] TMA box writes), K-major for Q/K and MN-major for V.
 //
 // Softmax keeps a per-row reference maximum that is only moved when the running maximum exceeds it
-// by more than 2^8 (the exponent offset is arbitrary as long as numerator and denominator share it),
+// by more than 2^32 (the exponent offset is arbitrary as long as numerator and denominator share it),
 // so the O accumulator in TMEM is rescaled rarely.  Row statistics are written in the layout of the
 // reference's Triton kernels: M = rowmax(s*scale)*log2(e), L = sum_j exp2(s_j*scale*log2e - M)
 // (kernels/sparse_attn/triton/attn_dense.py:209-227).
@@ -39,7 +40,9 @@ constexpr int kRegsSoftmax = 208, kRegsOther = 72;
 constexpr int kMaxSteps = 1024;  // per-slot KV tile list capacity (block-sparse: Lkv <= 131072)
 constexpr int kStages = 2;
 constexpr int kSchedStages = 2;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// Log2 units by which a row maximum may exceed the row's reference maximum before the reference moves
+// (and O is rescaled).  bf16 has the exponent range of fp32, so P = exp2(s - reference) <= 2^32 is safe.
+constexpr float kRescaleThreshold = 32.0f;
 
 enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2 };
 
@@ -591,9 +594,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 10) {
     // ============================================================ MMA issuer (one thread)
     setmaxnreg_dec<kRegsOther>();
-    if (lane == 0) {
+    // Every lane runs the (warp-uniform) bookkeeping; lane 0 alone issues the MMAs, commits and arrivals.
+    const uint32_t leader = lane == 0 ? 1u : 0u;
+    {
       bool ok = true;
-      const uint32_t qaddr = smem_u32(sQ), kaddr = smem_u32(sK), vaddr = smem_u32(sV);
+      // Descriptor words: the high word is the same for every operand tile, the low word is the tile's
+      // base plus (byte offset >> 4) of the stage and of the 16-element K step.
+      constexpr uint32_t DESC_HI = sw128_desc_hi(1024);
+      constexpr uint32_t TILE16 = SM::kTile >> 4;
+      const uint32_t q_lo = sw128_desc_lo(smem_u32(sQ), 16);
+      const uint32_t k_lo = sw128_desc_lo(smem_u32(sK), 16);
+      const uint32_t v_lo = sw128_desc_lo(smem_u32(sV), 16384);
       int kc = 0, vc = 0;        // K / V tiles consumed so far
       int nq_items = 0;          // items with steps (parity of q_full)
       int n_p[2] = {0, 0};       // P tiles consumed per slot (parity of p_full)
@@ -649,14 +660,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               tc_fence_after();
               const uint32_t tP = tmem_base + (uint32_t)s * 128u;
               const uint32_t tOs = tmem_base + TM_O + (uint32_t)s * D;
+              const uint32_t vb = v_lo + (uint32_t)pvs[s] * TILE16;
+              umma_ts_if(leader, tOs, tP, vb, DESC_HI, IDESC_PV, npv[s] > 0 ? 1u : 0u);
 #pragma unroll
-              for (int ks8 = 0; ks8 < 8; ++ks8) {
-                const uint64_t bd = make_sw128_desc(vaddr + pvs[s] * SM::kTile + ks8 * 2048, 16384, 1024);
-                umma_ts(tOs, tP + ks8 * 8, bd, IDESC_PV, (npv[s] > 0 || ks8 > 0) ? 1u : 0u);
-              }
+              for (int ks8 = 1; ks8 < 8; ++ks8)
+                umma_ts_if(leader, tOs, tP + ks8 * 8, vb + ks8 * 128, DESC_HI, IDESC_PV, 1u);
               ++npv[s];
               // release the V stage after its last user
-              if (!(s == 0 && prev.shared)) umma_commit(&bars->v_empty[pvs[s]]);
+              if (!(s == 0 && prev.shared)) umma_commit_if(leader, &bars->v_empty[pvs[s]]);
             }
             if (cur.has[s]) {
               if (!(s == 1 && cur.shared)) {
@@ -665,15 +676,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tc_fence_after();
               }
               const uint32_t tSs = tmem_base + (uint32_t)s * 128u;
+              const uint32_t qa = q_lo + (uint32_t)s * TILE16, kb = k_lo + (uint32_t)ks[s] * TILE16;
 #pragma unroll
               for (int kq = 0; kq < KSTEPS_QK; ++kq) {
-                const uint32_t koff = (kq >> 2) * 16384 + (kq & 3) * 32;
-                const uint64_t ad = make_sw128_desc(qaddr + s * SM::kTile + koff, 16, 1024);
-                const uint64_t bd = make_sw128_desc(kaddr + ks[s] * SM::kTile + koff, 16, 1024);
-                umma_ss(tSs, ad, bd, IDESC_QK, kq > 0 ? 1u : 0u);
+                const uint32_t koff = (kq >> 2) * 1024 + (kq & 3) * 2;  // (byte offset of the K step) >> 4
+                umma_ss_if(leader, tSs, qa + koff, DESC_HI, kb + koff, DESC_HI, IDESC_QK, kq > 0 ? 1u : 0u);
               }
-              umma_commit(&bars->s_full[s]);
-              if (!(s == 0 && cur.shared)) umma_commit(&bars->k_empty[ks[s]]);
+              umma_commit_if(leader, &bars->s_full[s]);
+              if (!(s == 0 && cur.shared)) umma_commit_if(leader, &bars->k_empty[ks[s]]);
             }
           }
           if (!ok) break;
@@ -681,22 +691,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pvs[0] = vs[0]; pvs[1] = vs[1]; pvp[0] = vp[0]; pvp[1] = vp[1];
         }
         if (!ok) break;
-        if (rounds > 0) umma_commit(&bars->q_empty);
+        if (rounds > 0) umma_commit_if(leader, &bars->q_empty);
         for (int s = 0; s < 2; ++s) {
           if (npv[s] > 0) {
-            umma_commit(&bars->o_full[s]);
+            umma_commit_if(leader, &bars->o_full[s]);
             ++n_o[s];
           }
         }
-        mbar_arrive(&bars->sched_empty[n % kSchedStages]);
+        if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
       }
       // TMEM must not be freed (nor the CTA retire) while an MMA is still in flight, also on abort.
-      umma_commit(&bars->mma_done);
-      const uint64_t t0 = globaltimer_ns();
-      while (!mbar_try_wait(&bars->mma_done, 0)) {
-        if (globaltimer_ns() - t0 > 2000000000ull) {
-          if (p.status) atomicCAS(p.status, 0, (int)DEV_TIMEOUT_DRAIN);
-          break;
+      if (lane == 0) {
+        umma_commit(&bars->mma_done);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->mma_done, 0)) {
+          if (globaltimer_ns() - t0 > 2000000000ull) {
+            if (p.status) atomicCAS(p.status, 0, (int)DEV_TIMEOUT_DRAIN);
+            break;
+          }
         }
       }
     }

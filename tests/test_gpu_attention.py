@@ -292,8 +292,9 @@ def test_full_size_properties(K):
     q, k, v = (t.cuda() for t in _qkv(B, H, Lq, Lkv, D, seed=0, peaked=True))
     scale = 1.0 / math.sqrt(D)
     dense, M, L = K.dense_attn_fwd(q, k, v, scale)
-    ref = torch.nn.functional.scaled_dot_product_attention(q[:1, :2], k[:1, :2], v[:1, :2], scale=scale)
-    assert (dense[:1, :2].float() - ref.float()).abs().max().item() <= O_MAX
+    ref = torch.nn.functional.scaled_dot_product_attention(q[:1, :2].float(), k[:1, :2].float(), v[:1, :2].float(),
+                                                           scale=scale)
+    assert (dense[:1, :2].float() - ref).abs().max().item() <= O_MAX
     # a block mask of all ones walks the same tiles in the same order as the dense kernel
     ones = torch.ones(32, 83, dtype=torch.bool, device="cuda")
     assert torch.equal(K.block_sparse_attn_fwd(q, k, v, ones, scale), dense)
