@@ -264,14 +264,51 @@ def run_ours(args):
     h2d = sum(t.numel() * t.element_size() for t in (q_pin, k_pin, v_pin, mask_pin))
     d2h = o_pin.numel() * o_pin.element_size()
 
+    # Three streams: step i's host->device copies, step i-1's kernel and step i-2's device->host copy run at
+    # the same time (PCIe is full duplex and much slower than the kernel), every step still moves all of its
+    # inputs from pinned host memory and its output back inside the timed region.
+    s_in, s_run, s_out = (torch.cuda.Stream(dev) for _ in range(3))
+    slots = [dict(q=torch.empty_like(q), k=torch.empty_like(k), v=torch.empty_like(v), m=torch.empty_like(mask),
+                  o=None, loaded=torch.cuda.Event(), ran=torch.cuda.Event(), stored=torch.cuda.Event())
+             for _ in range(2)]
+    step_no = [0]
+
     def e2e_step():
-        qd, kd, vd = (t.to(dev, non_blocking=True) for t in (q_pin, k_pin, v_pin))
-        md = mask_pin.to(dev, non_blocking=True)
-        o = ops.block_sparse_attn(qd, kd, vd, md, scale)
-        o_pin.copy_(o, non_blocking=True)
+        sl = slots[step_no[0] % 2]
+        step_no[0] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(sl["ran"])      # the kernel that last read these device buffers has finished
+            sl["q"].copy_(q_pin, non_blocking=True)
+            sl["k"].copy_(k_pin, non_blocking=True)
+            sl["v"].copy_(v_pin, non_blocking=True)
+            sl["m"].copy_(mask_pin, non_blocking=True)
+            sl["loaded"].record(s_in)
+        with torch.cuda.stream(s_run):
+            s_run.wait_event(sl["loaded"])
+            s_run.wait_event(sl["stored"])  # the previous output of this slot has left the device
+            sl["o"] = ops.block_sparse_attn(sl["q"], sl["k"], sl["v"], sl["m"], scale)
+            sl["ran"].record(s_run)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(sl["ran"])
+            o_pin.copy_(sl["o"], non_blocking=True)
+            sl["stored"].record(s_out)
+
+    def e2e_timed(iters, warm):
+        for _ in range(warm):
+            e2e_step()
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(iters):
+            e2e_step()
+        for st in (s_in, s_run, s_out):
+            torch.cuda.current_stream().wait_stream(st)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
 
     e2e_iters = max(3, min(args.steps, 20))
-    e2e_ms = timed(e2e_step, e2e_iters, warm=2)
+    e2e_ms = e2e_timed(e2e_iters, 2)
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -1,35 +1,42 @@
-// Device helpers shared by the attention kernels: swizzled tile addressing, the cp.async row
-// gather, and the register-level softmax pieces (3-input max, packed exp2 + bf16 packing).
+// Device helpers shared by the attention kernels: the cp.async row gather into a swizzled tile and the
+// register-level softmax pieces (3-input max, packed exp2 + bf16 packing).
 #pragma once
 
 #include "ptx.cuh"
 
 namespace lvar {
 
-// Swizzled byte offset of 16-byte chunk `c16` (0..D/8-1) of row `r` inside a [128][D] tile made of
-// [128][64] sub-tiles with the 128-byte TMA swizzle.
-__device__ __forceinline__ uint32_t sw128_offset(int r, int c16) {
-  return (uint32_t)((c16 >> 3) * 16384 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
+// Column-sparse attention gathers the 128 rows of KV tile `j` of an index list into a swizzled [128][D]
+// tile with 16-byte cp.async copies, one warp per tile.  Lane l copies rows l, l+32, l+64 and l+96 whole:
+// it reads its four indices (coalesced across the warp; gather_rows_of_tile, which the loaders call one
+// tile ahead so that the index latency is off the critical path), forms the four row pointers once, and
+// then issues nothing but copies (gather_tile); the 16-byte chunks of a row are consecutive cp.async of
+// the same lane and meet again in L1.  List positions past `cnt` read row 0 (their P columns are zero).
+__device__ __forceinline__ void gather_rows_of_tile(int (&kv)[4], const int32_t* idx, int cnt, int j, int Lkv,
+                                                    int lane, int* status) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int pos = j * 128 + i * 32 + lane;
+    int v = (pos < cnt) ? __ldg(idx + pos) : 0;
+    if ((unsigned)v >= (unsigned)Lkv) {
+      if (status) atomicCAS(status, 0, (int)DEV_BAD_INDEX);
+      v = 0;
+    }
+    kv[i] = v;
+  }
 }
-
-// One warp gathers the 128 rows of KV tile `j` of an index list into a swizzled [128][D] tile with
-// 16-byte cp.async copies.  List positions past `cnt` read row 0 (their P columns are zero).
 template <int D>
 __device__ __forceinline__ void gather_tile(uint32_t dst, const __nv_bfloat16* base, int64_t row_stride,
-                                            const int32_t* idx, int cnt, int j, int Lkv, int lane, int* status) {
-  constexpr int CH = D / 8;        // 16-byte chunks per row
-  constexpr int RPP = 32 / CH;     // rows per warp pass
-  const int c16 = lane % CH;
-#pragma unroll 4
-  for (int rr = 0; rr < 128; rr += RPP) {
-    const int r = rr + lane / CH;
-    const int pos = j * 128 + r;
-    int kv = (pos < cnt) ? __ldg(idx + pos) : 0;
-    if ((unsigned)kv >= (unsigned)Lkv) {
-      if (status) atomicCAS(status, 0, (int)DEV_BAD_INDEX);
-      kv = 0;
-    }
-    cp_async_16(dst + sw128_offset(r, c16), base + (int64_t)kv * row_stride + c16 * 8);
+                                            const int (&kv)[4], int lane) {
+  constexpr int CH = D / 8;  // 16-byte chunks per row
+  const uint32_t x = (uint32_t)(lane & 7);  // rows l + 32 i all have r % 8 == l % 8: one swizzle pattern per lane
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat16* src = base + (int64_t)kv[i] * row_stride;
+    const uint32_t drow = dst + (uint32_t)(i * 32 + lane) * 128u;
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+      cp_async_16_l1(drow + (uint32_t)(c >> 3) * 16384u + ((((uint32_t)c & 7u) ^ x) << 4), src + c * 8);
   }
 }
 

@@ -7,7 +7,8 @@
 // same round is loaded once (always the case for dense and column-sparse attention).
 //   warps 0-3   softmax warpgroup of slot 0 (thread = one query row = one TMEM lane)
 //   warps 4-7   softmax warpgroup of slot 1
-//   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp
+//   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp (each lane
+//               copies four whole rows; the tile's barrier takes one arrival per lane as its copies land)
 //   warp  9     V loader
 //   warp  10    allocates TMEM; lane 0 issues every tcgen05.mma (descriptor words precomputed, all lanes
 //               run the bookkeeping so that it stays out of a divergent branch)
@@ -435,7 +436,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bool ok = true;
     int kc = 0;       // K tiles issued so far (stage = kc % kStages)
     int nq_items = 0; // items with at least one step (parity of q_full / q_empty)
-    int pending = -1; // csp: stage whose cp.async group has been committed but not yet signalled
     const bool issuer = (MODE == MODE_CSP) || lane == 0;
     if (issuer) {
       for (int n = 0; ok; ++n) {
@@ -479,25 +479,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         } else {
           const int32_t* idx = p.indices + im.b * p.i_sb + im.h * p.i_sh + (int64_t)im.group * p.i_sg;
           const __nv_bfloat16* kbase = p.k + im.b * p.k_sb + im.h * p.k_sh;
+          int kv[4];
+          if (rounds > 0) gather_rows_of_tile(kv, idx, e.aux, 0, p.Lkv, lane, p.status);
           for (int j = 0; j < rounds; ++j) {
             const int st = kc % kStages;
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_empty[st], ((kc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
             if (!ok) break;
-            gather_tile<D>(smem_u32(sK + st * SM::kTile), kbase, p.k_sl, idx, e.aux, j, p.Lkv, lane, p.status);
-            cp_async_commit();
-            if (pending >= 0) {  // the previous tile has landed once at most one group is pending
-              cp_async_wait<1>();
-              fence_proxy_async_smem();
-              mbar_arrive(&bars->k_full[pending]);
-            }
-            pending = st;
+            gather_tile<D>(smem_u32(sK + st * SM::kTile), kbase, p.k_sl, kv, lane);
+            // each lane's arrival follows its own copies; nobody waits here (the MMA warp fences the proxies)
+            cp_async_mbar_arrive(&bars->k_full[st]);
+            if (j + 1 < rounds) gather_rows_of_tile(kv, idx, e.aux, j + 1, p.Lkv, lane, p.status);
             ++kc;
-          }
-          if (pending >= 0) {
-            cp_async_wait<0>();
-            fence_proxy_async_smem();
-            mbar_arrive(&bars->k_full[pending]);
-            pending = -1;
           }
         }
         if (!ok) break;
@@ -526,7 +518,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     setmaxnreg_dec<kRegsOther>();
     bool ok = true;
     int vc = 0;
-    int pending = -1;
     const bool issuer = (MODE == MODE_CSP) || lane == 0;
     if (issuer) {
       for (int n = 0; ok; ++n) {
@@ -556,25 +547,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         } else {
           const int32_t* idx = p.indices + im.b * p.i_sb + im.h * p.i_sh + (int64_t)im.group * p.i_sg;
           const __nv_bfloat16* vbase = p.v + im.b * p.v_sb + im.h * p.v_sh;
+          int kv[4];
+          if (rounds > 0) gather_rows_of_tile(kv, idx, e.aux, 0, p.Lkv, lane, nullptr);
           for (int j = 0; j < rounds; ++j) {
             const int st = vc % kStages;
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_empty[st], ((vc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
             if (!ok) break;
-            gather_tile<D>(smem_u32(sV + st * SM::kTile), vbase, p.v_sl, idx, e.aux, j, p.Lkv, lane, nullptr);
-            cp_async_commit();
-            if (pending >= 0) {
-              cp_async_wait<1>();
-              fence_proxy_async_smem();
-              mbar_arrive(&bars->v_full[pending]);
-            }
-            pending = st;
+            gather_tile<D>(smem_u32(sV + st * SM::kTile), vbase, p.v_sl, kv, lane);
+            cp_async_mbar_arrive(&bars->v_full[st]);
+            if (j + 1 < rounds) gather_rows_of_tile(kv, idx, e.aux, j + 1, p.Lkv, lane, nullptr);
             ++vc;
-          }
-          if (pending >= 0) {
-            cp_async_wait<0>();
-            fence_proxy_async_smem();
-            mbar_arrive(&bars->v_full[pending]);
-            pending = -1;
           }
         }
         if (!ok) break;
@@ -657,6 +639,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               ok = mbar_wait(&bars->p_full[s], n_p[s] & 1, wc, DEV_TIMEOUT_MMA);
               if (!ok) break;
               ++n_p[s];
+              // column-sparse: V came by cp.async (generic proxy), the MMA reads it through the async proxy
+              if (MODE == MODE_CSP) fence_proxy_async_smem();
               tc_fence_after();
               const uint32_t tP = tmem_base + (uint32_t)s * 128u;
               const uint32_t tOs = tmem_base + TM_O + (uint32_t)s * D;
@@ -673,6 +657,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               if (!(s == 1 && cur.shared)) {
                 ok = mbar_wait(&bars->k_full[ks[s]], kp[s], wc, DEV_TIMEOUT_MMA);
                 if (!ok) break;
+                if (MODE == MODE_CSP) fence_proxy_async_smem();
                 tc_fence_after();
               }
               const uint32_t tSs = tmem_base + (uint32_t)s * 128u;
