@@ -25,6 +25,15 @@ __device__ __forceinline__ void gather_rows_of_tile(int (&kv)[4], const int32_t*
     kv[i] = v;
   }
 }
+// True (on every lane) when the tile's 128 list entries are all inside the list and name 128 consecutive
+// keys kv[0] of lane 0, +1, ...: such a tile can be fetched with one TMA tile copy.
+__device__ __forceinline__ bool tile_is_run(const int (&kv)[4], int cnt, int j, int Lkv, int lane) {
+  const int first = __shfl_sync(0xffffffffu, kv[0], 0);
+  bool run = (j + 1) * 128 <= cnt && first + 128 <= Lkv;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) run = run && kv[i] == first + i * 32 + lane;
+  return __all_sync(0xffffffffu, run);
+}
 template <int D>
 __device__ __forceinline__ void gather_tile(uint32_t dst, const __nv_bfloat16* base, int64_t row_stride,
                                             const int (&kv)[4], int lane) {

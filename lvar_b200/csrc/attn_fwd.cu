@@ -179,10 +179,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tmQ);
-    if (MODE != MODE_CSP) {
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-    }
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
   }
   tc_fence_before();
   __syncthreads();
@@ -485,9 +483,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int st = kc % kStages;
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_empty[st], ((kc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
             if (!ok) break;
-            gather_tile<D>(smem_u32(sK + st * SM::kTile), kbase, p.k_sl, kv, lane);
-            // each lane's arrival follows its own copies; nobody waits here (the MMA warp fences the proxies)
-            cp_async_mbar_arrive(&bars->k_full[st]);
+            if (tile_is_run(kv, e.aux, j, p.Lkv, lane)) {
+              // 128 consecutive keys (the local band of a list): one tile copy instead of 2048 row pieces
+              if (lane == 0) {
+                mbar_arrive_expect_tx(&bars->k_full[st], SM::kTile);
+                for (int sub = 0; sub < NSUB; ++sub)
+                  tma_load_4d(sK + st * SM::kTile + sub * 16384, &tmK, &bars->k_full[st], sub * 64, kv[0], im.h, im.b);
+              } else {
+                mbar_arrive(&bars->k_full[st]);
+              }
+            } else {
+              gather_tile<D>(smem_u32(sK + st * SM::kTile), kbase, p.k_sl, kv, lane);
+              // each lane's arrival follows its own copies; nobody waits here (the MMA warp fences the proxies)
+              cp_async_mbar_arrive(&bars->k_full[st]);
+            }
             if (j + 1 < rounds) gather_rows_of_tile(kv, idx, e.aux, j + 1, p.Lkv, lane, p.status);
             ++kc;
           }
@@ -553,8 +562,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int st = vc % kStages;
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_empty[st], ((vc / kStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
             if (!ok) break;
-            gather_tile<D>(smem_u32(sV + st * SM::kTile), vbase, p.v_sl, kv, lane);
-            cp_async_mbar_arrive(&bars->v_full[st]);
+            if (tile_is_run(kv, e.aux, j, p.Lkv, lane)) {
+              if (lane == 0) {
+                mbar_arrive_expect_tx(&bars->v_full[st], SM::kTile);
+                for (int sub = 0; sub < NSUB; ++sub)
+                  tma_load_4d(sV + st * SM::kTile + sub * 16384, &tmV, &bars->v_full[st], sub * 64, kv[0], im.h, im.b);
+              } else {
+                mbar_arrive(&bars->v_full[st]);
+              }
+            } else {
+              gather_tile<D>(smem_u32(sV + st * SM::kTile), vbase, p.v_sl, kv, lane);
+              cp_async_mbar_arrive(&bars->v_full[st]);
+            }
             if (j + 1 < rounds) gather_rows_of_tile(kv, idx, e.aux, j + 1, p.Lkv, lane, nullptr);
             ++vc;
           }

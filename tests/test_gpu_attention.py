@@ -241,6 +241,40 @@ def test_csp_attn_all_keys_equals_dense(K):
     assert (o.float() - dense.float()).abs().max().item() <= 8e-3
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_csp_attn_lists_with_runs_of_consecutive_keys(K, D):
+    """Tiles of 128 consecutive keys (the local band of a CS4A list) take the tile-copy path, the other tiles
+    the row gather; a run that ends at the last key, one that is cut by the count and one that is off by
+    one key in the middle sit next to them."""
+    from oracle import attention as oa
+    B, H, Lq, Lkv, bm = 1, 2, 512, 1000, 256
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=11)
+    G = Lq // bm
+    g = torch.Generator().manual_seed(11)
+    run = lambda a: torch.arange(a, a + 128, dtype=torch.int32)
+    rnd = lambda: torch.randint(0, Lkv, (128,), generator=g, dtype=torch.int32)
+    broken = run(300).clone()
+    broken[77] = 5
+    lists = [
+        torch.cat([rnd(), run(417), run(Lkv - 128), rnd(), run(40)]),       # runs between gathers, run at the end of K
+        torch.cat([run(0), broken, run(545), run(100), rnd()]),             # a run with one foreign key
+    ]
+    idx = torch.zeros(B, H, G, Lkv, dtype=torch.int32)
+    counts = torch.zeros(B, H, G, dtype=torch.int32)
+    for h in range(H):
+        for gi in range(G):
+            li = lists[(h + gi) % 2]
+            idx[0, h, gi, :li.numel()] = li
+            counts[0, h, gi] = li.numel() if (h + gi) % 2 == 0 else li.numel() - 60  # cut inside the last tile
+    o_in = torch.randn(B, H, Lq, D, generator=g).bfloat16()
+    st = K.new_status("cuda")
+    o = K.csp_attn_fwd(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), counts.cuda(), o_in.cuda(), 1, bm, status=st)
+    _ok_status(K, st)
+    ref = oa.csp_attn(q, k, v, None, idx, counts, o_in, 1, bm=bm)
+    d = (o.float().cpu() - ref.float()).abs()
+    assert d.max().item() <= 3.2e-2 and d.mean().item() <= O_MEAN
+
+
 def test_csp_attn_out_of_range_index_is_reported(K):
     q, k, v = _qkv(1, 1, 128, 200, 64, seed=6)
     idx = torch.arange(128, dtype=torch.int32).view(1, 1, 1, 128).clone()
