@@ -234,6 +234,21 @@ def run_ours(args):
     colsum_ms = timed(lambda: K.colsum_fwd(q, k, M, L, BLOCK, scale), 10)
     mask_ms = timed(lambda: K.build_block_mask(K.block_scores(cs, BLOCK), always, K_TOTAL), 10)
 
+    # ---- the column-sparse kernel on a list shaped like a last-scale sparse step: per 256-row query group
+    # 1664 scattered keys (the decision scale's top-k) followed by a band of 512 consecutive keys
+    csp_bm, csp_top, csp_band = 256, 1664, 512
+    n_groups = (LQ + csp_bm - 1) // csp_bm
+    gen = torch.Generator(device=dev).manual_seed(1)
+    top = torch.rand(B, H, n_groups, LKV, device=dev, generator=gen).argsort(-1)[..., :csp_top].to(torch.int32)
+    start = torch.randint(0, LKV - csp_band, (B, H, n_groups, 1), device=dev, generator=gen)
+    band = (start + torch.arange(csp_band, device=dev)).to(torch.int32)
+    csp_lists = torch.zeros(B, H, n_groups, LKV, dtype=torch.int32, device=dev)
+    csp_lists[..., :csp_top + csp_band] = torch.cat([top, band], dim=-1)
+    csp_counts = torch.full((B, H, n_groups), csp_top + csp_band, dtype=torch.int32, device=dev)
+    csp_ms = timed(lambda: K.csp_attn_fwd(q, k, v, csp_lists, csp_counts, o_dense, 1, csp_bm, scale), 10)
+    csp_flops = 4.0 * B * H * LQ * (csp_top + csp_band) * D
+    del top, band, csp_lists, csp_counts
+
     # ---- timed region: K steps of block-sparse attention, inputs resident in HBM
     step = lambda: K.block_sparse_attn_fwd(q, k, v, mask, scale)  # noqa: E731
     for _ in range(max(3, args.warmup)):
@@ -338,7 +353,9 @@ def run_ours(args):
         "clocks": clocks.summary(),
         "extra": {"dense_attn_ms": dense_ms, "dense_attn_tflops": dense_flops / dense_ms / 1e9,
                   "colsum_sweep_us": colsum_ms * 1e3, "colsum_over_dense_attn": colsum_ms / dense_ms,
-                  "mask_build_us": mask_ms * 1e3, "density": K_TOTAL / nk},
+                  "mask_build_us": mask_ms * 1e3, "density": K_TOTAL / nk,
+                  "csp_attn_us": csp_ms * 1e3, "csp_attn_tflops": csp_flops / csp_ms / 1e9,
+                  "csp_attn_workload": f"{csp_top} scattered + {csp_band} consecutive keys per {csp_bm}-row group"},
     }
     if world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
