@@ -170,6 +170,27 @@ int lvar_sparse_step_lists(const int32_t* src, const int32_t* remap, const int32
                            int64_t src_bh_stride, int32_t Gk, int32_t cnt, int32_t band_count, int32_t k_len,
                            int32_t out_cols, int32_t count_value, lvar_stream_t stream);
 
+/* ScaleKV cache compaction (models/scalekv/scale_kv.py:163-301, ScaleKVCluster.update_kv), device part.
+ * window: int32 [w] distinct key indices of the current scale's window grid (same for every batch and head).
+ *
+ * lvar_scalekv_scores: scores fp32 [B*H, Lkv] = sum over the w window queries (query row
+ * clamp(window[i] - offset, 0, Lq-1)) of bf16(bf16(q_i . k_j) / sqrt(D)), rounded to bf16, -inf on the
+ * window's own columns: the reference's matmul / sqrt(head_dim), masked_fill(-inf) and sum(dim=2) on bf16
+ * tensors (scale_kv.py:245-253).
+ * lvar_scalekv_pool: pooled fp32 [rows, Lkv] = max_pool1d / avg_pool1d(scores, ksize, padding ksize/2,
+ * stride 1) (scale_kv.py:255-258) with the window columns then set to +inf, so that
+ * lvar_topk_indices(pooled, k = max_capacity, ascending_index = 1) yields the reference's
+ * sort(cat(top-(max_capacity - w) of the non-window columns, window)) (scale_kv.py:260-276).
+ * lvar_gather_rows: dst bf16 [B,H,n,D] contiguous = src[b,h,clamp(idx[b*H+h, i]),:] (scale_kv.py:288-294);
+ * idx int32 rows of idx_row_stride entries.  q, k, src: bf16 with element strides, last dim contiguous. */
+int lvar_scalekv_scores(const void* q, const void* k, const int32_t* window, float* scores, int32_t B, int32_t H,
+                        int32_t Lq, int32_t Lkv, int32_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb,
+                        int64_t k_sh, int64_t k_sl, int32_t w, int32_t offset, lvar_stream_t stream);
+int lvar_scalekv_pool(const float* scores, const int32_t* window, int32_t w, float* pooled, int64_t rows, int32_t Lkv,
+                      int32_t ksize, int32_t avg, lvar_stream_t stream);
+int lvar_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t B, int32_t H, int32_t L, int32_t n,
+                     int32_t D, int64_t s_sb, int64_t s_sh, int64_t s_sl, int64_t idx_row_stride, lvar_stream_t stream);
+
 /* Bilinear (align_corners = false) resize of an attention-output cache between two square token grids:
  * src bf16 [BH, src_side^2, D] -> dst bf16 [BH, dst_side^2, D] (strides in elements, D a multiple of 8).
  * Replaces upsample_Ocache(o, L_src, L_tgt, mode='2d', upsample_mode='bilinear')

@@ -74,6 +74,10 @@ _SIGNATURES = {
                                       [C.c_int32, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p]),
     "lvar_sparse_step_lists": (C.c_int, [C.c_void_p] * 5 + [C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int64] +
                                [C.c_int32] * 6 + [C.c_void_p]),
+    "lvar_scalekv_scores": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 5 + [C.c_int64] * 6 + [C.c_int32] * 2 + [C.c_void_p]),
+    "lvar_scalekv_pool": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                    C.c_int32, C.c_void_p]),
+    "lvar_gather_rows": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 5 + [C.c_int64] * 4 + [C.c_void_p]),
     "lvar_upsample_ocache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32] +
                              [C.c_int64] * 4 + [C.c_void_p]),
     "lvar_last_error": (C.c_char_p, []),

@@ -84,6 +84,13 @@ int launch_sparse_step_lists(const int32_t* src, const int32_t* remap, const int
                              int32_t* counts, int64_t BH, int Gs, int src_cols, int64_t src_g_stride,
                              int64_t src_bh_stride, int Gk, int cnt, int band_count, int k_len, int out_cols,
                              int count_value, cudaStream_t stream);
+int launch_scalekv_scores(const void* q, const void* k, const int32_t* window, float* scores, int B, int H, int Lq,
+                          int Lkv, int D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh,
+                          int64_t k_sl, int w, int offset, cudaStream_t stream);
+int launch_scalekv_pool(const float* scores, const int32_t* window, int w, float* pooled, int64_t rows, int Lkv,
+                        int ksize, int avg, cudaStream_t stream);
+int launch_gather_rows(const void* src, const int32_t* idx, void* dst, int B, int H, int L, int n, int D, int64_t s_sb,
+                       int64_t s_sh, int64_t s_sl, int64_t idx_row_stride, cudaStream_t stream);
 int launch_upsample_ocache(const void* src, void* dst, int64_t BH, int src_side, int dst_side, int D,
                            int64_t src_bh_stride, int64_t src_row_stride, int64_t dst_bh_stride,
                            int64_t dst_row_stride, cudaStream_t stream);
@@ -98,6 +105,24 @@ int lvar_sparse_step_lists(const int32_t* src, const int32_t* remap, const int32
                            int32_t out_cols, int32_t count_value, lvar_stream_t stream) {
   return lvar::launch_sparse_step_lists(src, remap, band, out, counts, BH, Gs, src_cols, src_g_stride, src_bh_stride,
                                         Gk, cnt, band_count, k_len, out_cols, count_value, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_scalekv_scores(const void* q, const void* k, const int32_t* window, float* scores, int32_t B, int32_t H,
+                        int32_t Lq, int32_t Lkv, int32_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb,
+                        int64_t k_sh, int64_t k_sl, int32_t w, int32_t offset, lvar_stream_t stream) {
+  return lvar::launch_scalekv_scores(q, k, window, scores, B, H, Lq, Lkv, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, w, offset,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+int lvar_scalekv_pool(const float* scores, const int32_t* window, int32_t w, float* pooled, int64_t rows, int32_t Lkv,
+                      int32_t ksize, int32_t avg, lvar_stream_t stream) {
+  return lvar::launch_scalekv_pool(scores, window, w, pooled, rows, Lkv, ksize, avg, static_cast<cudaStream_t>(stream));
+}
+
+int lvar_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t B, int32_t H, int32_t L, int32_t n,
+                     int32_t D, int64_t s_sb, int64_t s_sh, int64_t s_sl, int64_t idx_row_stride, lvar_stream_t stream) {
+  return lvar::launch_gather_rows(src, idx, dst, B, H, L, n, D, s_sb, s_sh, s_sl, idx_row_stride,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int lvar_upsample_ocache(const void* src, void* dst, int64_t BH, int32_t src_side, int32_t dst_side, int32_t D,

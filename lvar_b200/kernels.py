@@ -330,3 +330,49 @@ def sparse_step_lists(inds: torch.Tensor, remap: torch.Tensor, band: Optional[to
                                      int(cnt + band_count if count_value is None else count_value),
                                      _stream_ptr(inds.device)))
     return out, counts
+
+
+def scalekv_scores(q: torch.Tensor, k: torch.Tensor, window: torch.Tensor, offset: int) -> torch.Tensor:
+    """ScaleKV window scores: fp32 [B,H,Lkv], -inf on the window's own columns.  q bf16 [B,H,Lq,D],
+    k bf16 [B,H,Lkv,D], window int32 [w] (distinct key indices); the window queries are the query rows
+    clamp(window - offset, 0, Lq - 1)."""
+    _require_cuda_bf16("q", q)
+    _require_cuda_bf16("k", k)
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    _require(window.is_cuda and window.dtype == torch.int32 and window.dim() == 1, "window must be CUDA int32 [w]")
+    window = window.contiguous()
+    scores = torch.empty((B, H, Lkv), dtype=torch.float32, device=q.device)
+    check(lib.lvar_scalekv_scores(q.data_ptr(), k.data_ptr(), window.data_ptr(), scores.data_ptr(), B, H, Lq, Lkv, D,
+                                  q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                  window.shape[0], int(offset), _stream_ptr(q.device)))
+    return scores
+
+
+def scalekv_pool(scores: torch.Tensor, window: torch.Tensor, kernel_size: int, pooling: str) -> torch.Tensor:
+    """max_pool1d / avg_pool1d(scores, kernel_size, padding kernel_size//2, stride 1) with the window columns
+    then raised to +inf (see lvar_scalekv_pool)."""
+    _require(scores.is_cuda and scores.dtype == torch.float32 and scores.is_contiguous(),
+             "scores must be a contiguous CUDA float32 tensor")
+    _require(pooling in ("maxpool", "avgpool"), "pooling must be 'maxpool' or 'avgpool'")
+    Lkv = scores.shape[-1]
+    rows = scores.numel() // Lkv
+    pooled = torch.empty_like(scores)
+    check(lib.lvar_scalekv_pool(scores.data_ptr(), window.data_ptr(), window.shape[0], pooled.data_ptr(), rows, Lkv,
+                                int(kernel_size), int(pooling == "avgpool"), _stream_ptr(scores.device)))
+    return pooled
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """src bf16 [B,H,L,D], idx int32 [B,H,n] -> bf16 [B,H,n,D] = src[b,h,clamp(idx),:]."""
+    _require_cuda_bf16("src", src)
+    B, H, L, D = src.shape
+    _require(idx.is_cuda and idx.dtype == torch.int32 and idx.dim() == 3 and idx.shape[:2] == (B, H),
+             "idx must be CUDA int32 [B,H,n]")
+    idx = idx.contiguous()
+    n = idx.shape[2]
+    dst = torch.empty((B, H, n, D), dtype=src.dtype, device=src.device)
+    if n > 0:
+        check(lib.lvar_gather_rows(src.data_ptr(), idx.data_ptr(), dst.data_ptr(), B, H, L, n, D, src.stride(0),
+                                   src.stride(1), src.stride(2), n, _stream_ptr(src.device)))
+    return dst

@@ -41,3 +41,8 @@ def golden_indices():
 @pytest.fixture(scope="session")
 def golden_csla():
     return load_golden("csla_ref.npz")
+
+
+@pytest.fixture(scope="session")
+def golden_scalekv():
+    return load_golden("scalekv_ref.npz")

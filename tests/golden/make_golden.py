@@ -142,6 +142,48 @@ def make_csla(ref: Path) -> dict:
     return out
 
 
+def make_scalekv(ref: Path) -> dict:
+    """Runs the reference's ScaleKVCluster.update_kv (models/scalekv/scale_kv.py:12-301) on the CPU.  The class
+    is compiled out of the file because the module's import of the model package does not resolve."""
+    import math
+    import warnings
+    import torch.nn.functional as F
+    src = (ref / "models/scalekv/scale_kv.py").read_text()
+    cls = [n for n in ast.parse(src).body if isinstance(n, ast.ClassDef) and n.name == "ScaleKVCluster"][0]
+    ns = {"torch": torch, "F": F, "math": math, "warnings": warnings}
+    exec(compile(ast.Module(body=[cls], type_ignores=[]), "scale_kv.ScaleKVCluster", "exec"), ns)
+    Cluster = ns["ScaleKVCluster"]
+    tokens = [1, 4, 16, 36, 64, 144, 256, 400, 576, 1024, 1600, 2304, 4096]
+    out = {}
+    cases = (("a", torch.float32, 6, 300, "maxpool", 64), ("b", torch.float32, 7, 350, "avgpool", 128),
+             ("c", torch.bfloat16, 6, 300, "maxpool", 64), ("d", torch.bfloat16, 7, 420, "maxpool", 128))
+    for name, dtype, scale_ind, cap, pooling, D in cases:
+        gen = torch.Generator().manual_seed(100 + scale_ind)  # cases of one scale share their inputs
+        B, H = 1, 2
+        key_len, Lq = sum(tokens[:scale_ind + 1]), tokens[scale_ind]
+        q = _bf16_exact(B, H, Lq, D, gen=gen)
+        k = _bf16_exact(B, H, key_len, D, gen=gen)
+        v = _bf16_exact(B, H, key_len, D, gen=gen)
+        cluster = Cluster([[cap] * 4 for _ in range(16)], window_size=16, base_capacity=121, kernel_size=5,
+                          pooling=pooling, layer_idx=1)
+        with warnings.catch_warnings():
+            warnings.simplefilter("error")
+            ko, vo = cluster.update_kv(k.to(dtype), q.to(dtype), v.to(dtype), scale_ind)
+        assert ko.shape == (B, H, cap, D)
+        window = cluster._select_window_indices(Lq, key_len - Lq, "cpu", B, H, key_len)[0, 0]
+        # the indices the reference gathered: every key row is distinct, so rows identify them
+        idx = torch.empty(B, H, cap, dtype=torch.int64)
+        for b in range(B):
+            for h in range(H):
+                rows = {tuple(r.tolist()): j for j, r in enumerate(k[b, h].to(dtype).float())}
+                idx[b, h] = torch.tensor([rows[tuple(r.tolist())] for r in ko[b, h].float()])
+                assert torch.equal(vo[b, h].float(), v[b, h].to(dtype).float()[idx[b, h]])
+        out[f"s{scale_ind}_q"], out[f"s{scale_ind}_k"], out[f"s{scale_ind}_v"] = q, k, v
+        out[f"{name}_window"], out[f"{name}_idx"] = window, idx
+        out[f"{name}_meta"] = torch.tensor([scale_ind, cap, int(pooling == "avgpool"), int(dtype == torch.bfloat16)])
+    return out
+
+
 def main() -> None:
     ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     _install_stubs(ref)
@@ -153,6 +195,7 @@ def main() -> None:
         "attention_ref.npz": make_attention(ref_ops, ref_colsum, ref_csp),
         "indices_ref.npz": make_indices(sa),
         "csla_ref.npz": make_csla(ref),
+        "scalekv_ref.npz": make_scalekv(ref),
     }
     for name, d in groups.items():
         arrays = {}
