@@ -191,6 +191,20 @@ int lvar_scalekv_pool(const float* scores, const int32_t* window, int32_t w, flo
 int lvar_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t B, int32_t H, int32_t L, int32_t n,
                      int32_t D, int64_t s_sb, int64_t s_sh, int64_t s_sl, int64_t idx_row_stride, lvar_stream_t stream);
 
+/* QKV prologue of a self-attention layer during generation, fused: L2-normalise q and k over the head
+ * dimension (eps 1e-12), scale q by scale_mul[h], rotate both with the 2-D RoPE table rows
+ * rope_start .. rope_start+L-1 (cos/sin fp32 [*, c/2], pairs (2i, 2i+1)), write q as bf16 [B,H,L,c] and append
+ * k and v at row cache_pos of bf16 caches [B,H,cap,c] (models/sparvar/basic_sparvar.py:321-350: F.normalize,
+ * .mul(scale_mul), apply_rotary_emb, torch.cat onto cached_k / cached_v, and the q.to(v.dtype) / k.to(v.dtype)
+ * at the attention call sites :371-384; models/infinity/basic_infinity.py:111-133).
+ * qkv: bf16 projection output, element (b, l, which, h, e) at b*s_b + l*s_l + which*s_w + h*s_h + e.
+ * scale_mul NULL: no normalisation and no scale (cos_attn off); rope_cos/rope_sin NULL: no rotation. */
+int lvar_qkv_prologue(const void* qkv, int64_t s_b, int64_t s_l, int64_t s_w, int64_t s_h, const float* scale_mul,
+                      const float* rope_cos, const float* rope_sin, int32_t rope_start, void* q_out, int64_t q_sb,
+                      int64_t q_sh, int64_t q_sl, void* k_cache, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                      void* v_cache, int64_t v_sb, int64_t v_sh, int64_t v_sl, int32_t cache_pos, int32_t B, int32_t L,
+                      int32_t H, int32_t c, lvar_stream_t stream);
+
 /* Bilinear (align_corners = false) resize of an attention-output cache between two square token grids:
  * src bf16 [BH, src_side^2, D] -> dst bf16 [BH, dst_side^2, D] (strides in elements, D a multiple of 8).
  * Replaces upsample_Ocache(o, L_src, L_tgt, mode='2d', upsample_mode='bilinear')

@@ -78,6 +78,9 @@ _SIGNATURES = {
     "lvar_scalekv_pool": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                     C.c_int32, C.c_void_p]),
     "lvar_gather_rows": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 5 + [C.c_int64] * 4 + [C.c_void_p]),
+    "lvar_qkv_prologue": (C.c_int, [C.c_void_p] + [C.c_int64] * 4 + [C.c_void_p] * 3 + [C.c_int32] +
+                          [C.c_void_p] + [C.c_int64] * 3 + [C.c_void_p] + [C.c_int64] * 3 + [C.c_void_p] + [C.c_int64] * 3 +
+                          [C.c_int32] * 5 + [C.c_void_p]),
     "lvar_upsample_ocache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32] +
                              [C.c_int64] * 4 + [C.c_void_p]),
     "lvar_last_error": (C.c_char_p, []),

@@ -91,6 +91,11 @@ int launch_scalekv_pool(const float* scores, const int32_t* window, int w, float
                         int ksize, int avg, cudaStream_t stream);
 int launch_gather_rows(const void* src, const int32_t* idx, void* dst, int B, int H, int L, int n, int D, int64_t s_sb,
                        int64_t s_sh, int64_t s_sl, int64_t idx_row_stride, cudaStream_t stream);
+int launch_qkv_prologue(const void* qkv, int64_t s_b, int64_t s_l, int64_t s_w, int64_t s_h, const float* scale_mul,
+                        const float* rope_cos, const float* rope_sin, int rope_start, void* q_out, int64_t q_sb,
+                        int64_t q_sh, int64_t q_sl, void* k_cache, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                        void* v_cache, int64_t v_sb, int64_t v_sh, int64_t v_sl, int cache_pos, int B, int L, int H,
+                        int c, cudaStream_t stream);
 int launch_upsample_ocache(const void* src, void* dst, int64_t BH, int src_side, int dst_side, int D,
                            int64_t src_bh_stride, int64_t src_row_stride, int64_t dst_bh_stride,
                            int64_t dst_row_stride, cudaStream_t stream);
@@ -123,6 +128,16 @@ int lvar_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t B, 
                      int32_t D, int64_t s_sb, int64_t s_sh, int64_t s_sl, int64_t idx_row_stride, lvar_stream_t stream) {
   return lvar::launch_gather_rows(src, idx, dst, B, H, L, n, D, s_sb, s_sh, s_sl, idx_row_stride,
                                   static_cast<cudaStream_t>(stream));
+}
+
+int lvar_qkv_prologue(const void* qkv, int64_t s_b, int64_t s_l, int64_t s_w, int64_t s_h, const float* scale_mul,
+                      const float* rope_cos, const float* rope_sin, int32_t rope_start, void* q_out, int64_t q_sb,
+                      int64_t q_sh, int64_t q_sl, void* k_cache, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                      void* v_cache, int64_t v_sb, int64_t v_sh, int64_t v_sl, int32_t cache_pos, int32_t B, int32_t L,
+                      int32_t H, int32_t c, lvar_stream_t stream) {
+  return lvar::launch_qkv_prologue(qkv, s_b, s_l, s_w, s_h, scale_mul, rope_cos, rope_sin, rope_start, q_out, q_sb, q_sh,
+                                   q_sl, k_cache, k_sb, k_sh, k_sl, v_cache, v_sb, v_sh, v_sl, cache_pos, B, L, H, c,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 int lvar_upsample_ocache(const void* src, void* dst, int64_t BH, int32_t src_side, int32_t dst_side, int32_t D,

@@ -376,3 +376,37 @@ def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         check(lib.lvar_gather_rows(src.data_ptr(), idx.data_ptr(), dst.data_ptr(), B, H, L, n, D, src.stride(0),
                                    src.stride(1), src.stride(2), n, _stream_ptr(src.device)))
     return dst
+
+
+def qkv_prologue(qkv: torch.Tensor, scale_mul: Optional[torch.Tensor], rope_cos: Optional[torch.Tensor],
+                 rope_sin: Optional[torch.Tensor], rope_start: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 cache_pos: int) -> torch.Tensor:
+    """Fused L2-normalise / per-head scale / 2-D RoPE / KV-cache append.  qkv bf16 [B,L,3,H,c] (any strides with
+    a contiguous last dimension), scale_mul fp32 [H] or None, rope tables fp32 [P, c/2] or None; k_cache and
+    v_cache bf16 [B,H,cap,c] receive rows cache_pos .. cache_pos+L-1.  Returns q bf16 [B,H,L,c]."""
+    _require(qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 5 and qkv.shape[2] == 3 and
+             qkv.stride(-1) == 1, "qkv must be a CUDA bfloat16 [B,L,3,H,c] tensor with a contiguous last dimension")
+    B, L, _, H, c = qkv.shape
+    for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
+        _require_cuda_bf16(name, t)
+        _require(t.shape[0] == B and t.shape[1] == H and t.shape[3] == c and cache_pos + L <= t.shape[2],
+                 f"{name} must be [B,H,cap,c] with room for rows {cache_pos}..{cache_pos + L - 1}")
+    if scale_mul is not None:
+        _require(scale_mul.is_cuda and scale_mul.dtype == torch.float32 and scale_mul.numel() == H,
+                 "scale_mul must be CUDA float32 with H entries")
+        scale_mul = scale_mul.reshape(H).contiguous()
+    if rope_cos is not None:
+        for t in (rope_cos, rope_sin):
+            _require(t is not None and t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and
+                     t.shape[1] == c // 2 and t.is_contiguous() and rope_start + L <= t.shape[0],
+                     "rope tables must be contiguous CUDA float32 [P, c/2] covering rope_start+L rows")
+    q = torch.empty((B, H, L, c), dtype=torch.bfloat16, device=qkv.device)
+    check(lib.lvar_qkv_prologue(qkv.data_ptr(), qkv.stride(0), qkv.stride(1), qkv.stride(2), qkv.stride(3),
+                                scale_mul.data_ptr() if scale_mul is not None else None,
+                                rope_cos.data_ptr() if rope_cos is not None else None,
+                                rope_sin.data_ptr() if rope_cos is not None else None, int(rope_start),
+                                q.data_ptr(), q.stride(0), q.stride(1), q.stride(2),
+                                k_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
+                                v_cache.data_ptr(), v_cache.stride(0), v_cache.stride(1), v_cache.stride(2),
+                                int(cache_pos), B, L, H, c, _stream_ptr(qkv.device)))
+    return q

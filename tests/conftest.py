@@ -46,3 +46,8 @@ def golden_csla():
 @pytest.fixture(scope="session")
 def golden_scalekv():
     return load_golden("scalekv_ref.npz")
+
+
+@pytest.fixture(scope="session")
+def golden_prologue():
+    return load_golden("prologue_ref.npz")

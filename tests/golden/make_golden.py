@@ -184,6 +184,42 @@ def make_scalekv(ref: Path) -> dict:
     return out
 
 
+def make_prologue(ref: Path) -> dict:
+    """F.normalize + the reference's own precompute_rope2d_freqs_grid / apply_rotary_emb
+    (models/infinity/basic_infinity.py:42-133, compiled out of the file: the module imports flash-attn)."""
+    import torch.nn.functional as F
+    src = (ref / "models/infinity/basic_infinity.py").read_text()
+    fns = [n for n in ast.parse(src).body
+           if isinstance(n, ast.FunctionDef) and n.name in ("precompute_rope2d_freqs_grid", "apply_rotary_emb")]
+    assert len(fns) == 2
+    ns = {"torch": torch, "np": np, "F": F}
+    exec(compile(ast.Module(body=fns, type_ignores=[]), "basic_infinity.rope", "exec"), ns)
+    out = {}
+    sched = [(1, s, s) for s in SCALES]
+    for name, c, scale_ind in (("a", 64, 3), ("b", 128, 5)):
+        grid = ns["precompute_rope2d_freqs_grid"](dim=c, dynamic_resolution_h_w={1.0: {"1M": {"scales": sched}}},
+                                                  rope2d_normalized_by_hw=2, pad_to_multiplier=1)
+        gen = torch.Generator().manual_seed(50 + c)
+        B, H, L = 2, 3, SCALES[scale_ind] ** 2
+        qkv = _bf16_exact(B, L, 3, H, c, gen=gen)
+        scale_mul = torch.rand(H, generator=gen) * 8 + 1
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3).bfloat16() for i in range(3))
+        # as SelfAttention.forward under autocast: the norm is taken in fp32, so q and k become fp32
+        qn = F.normalize(q.float(), dim=-1, eps=1e-12).mul(scale_mul.view(1, H, 1, 1)).contiguous()
+        kn = F.normalize(k.float(), dim=-1, eps=1e-12).contiguous()
+        qr, kr = ns["apply_rotary_emb"](qn, kn, sched, grid, 1, 2, scale_ind)
+        table = grid[str(tuple(sched))]
+        out[f"{name}_qkv"] = qkv.reshape(B, L, 3 * H * c)
+        out[f"{name}_scale_mul"] = scale_mul
+        out[f"{name}_q_out"], out[f"{name}_k_out"] = qr.bfloat16().float(), kr.bfloat16().float()
+        used = sum(x * x for x in SCALES[:scale_ind + 1])
+        # the table rows this case uses, and the last 64 rows of the table (64 x 64 map) to pin the builder
+        out[f"{name}_cos"], out[f"{name}_sin"] = table[0, 0, 0, 0, :used], table[1, 0, 0, 0, :used]
+        out[f"{name}_cos_tail"], out[f"{name}_sin_tail"] = table[0, 0, 0, 0, -64:], table[1, 0, 0, 0, -64:]
+        out[f"{name}_meta"] = torch.tensor([B, L, H, c, scale_ind])
+    return out
+
+
 def main() -> None:
     ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     _install_stubs(ref)
@@ -196,6 +232,7 @@ def main() -> None:
         "indices_ref.npz": make_indices(sa),
         "csla_ref.npz": make_csla(ref),
         "scalekv_ref.npz": make_scalekv(ref),
+        "prologue_ref.npz": make_prologue(ref),
     }
     for name, d in groups.items():
         arrays = {}
@@ -203,7 +240,7 @@ def main() -> None:
             a = v.numpy() if isinstance(v, torch.Tensor) else np.asarray(v)
             if a.dtype == np.float64:
                 a = a.astype(np.float32)
-            if k.endswith(("_q", "_k", "_v")) and a.dtype == np.float32:
+            if k.endswith(("_q", "_k", "_v", "_qkv", "_q_out", "_k_out")) and a.dtype == np.float32:
                 # inputs are bf16-exact: keep the upper 16 bits only (the tests widen them back)
                 a = (a.view(np.uint32) >> 16).astype(np.uint16)
             if a.dtype == np.int64 and a.size > 64 and np.abs(a).max() < 2**31:
