@@ -221,8 +221,7 @@ def run_ours(args):
         return a.elapsed_time(b) / iters
 
     # ---- scoring + mask construction (once per decision in the model; timed here for the record)
-    o_dense, M, L = K.dense_attn_fwd(q, k, v, scale)
-    cs = K.colsum_fwd(q, k, M, L, BLOCK, scale)
+    o_dense, cs, M, L = K.dense_colsum_attn_fwd(q, k, v, scale, return_stats=True)
     scores = K.block_scores(cs, BLOCK)
     always = P.sink_local_blocks(nq, nk, BLOCK, SINK_TOKENS, Q_OFFSET, 0, LQ).to(dev)
     mask = K.build_block_mask(scores, always, K_TOTAL)
@@ -232,6 +231,7 @@ def run_ours(args):
     dense_flops = 4.0 * B * H * LQ * LKV * D
     dense_ms = timed(lambda: K.dense_attn_fwd(q, k, v, scale), 10)
     colsum_ms = timed(lambda: K.colsum_fwd(q, k, M, L, BLOCK, scale), 10)
+    fused_ms = timed(lambda: K.dense_colsum_attn_fwd(q, k, v, scale), 10)  # attention + column sums, one launch
     mask_ms = timed(lambda: K.build_block_mask(K.block_scores(cs, BLOCK), always, K_TOTAL), 10)
 
     # ---- the column-sparse kernel on a list shaped like a last-scale sparse step: per 256-row query group
@@ -352,7 +352,9 @@ def run_ours(args):
         "gpu_launches": args.steps,
         "clocks": clocks.summary(),
         "extra": {"dense_attn_ms": dense_ms, "dense_attn_tflops": dense_flops / dense_ms / 1e9,
-                  "colsum_sweep_us": colsum_ms * 1e3, "colsum_over_dense_attn": colsum_ms / dense_ms,
+                  "colsum_sweep_us": colsum_ms * 1e3, "dense_colsum_fused_ms": fused_ms,
+                  "colsum_over_dense_attn": (fused_ms - dense_ms) / dense_ms,
+                  "colsum_over_dense_attn_separate_kernels": colsum_ms / dense_ms,
                   "mask_build_us": mask_ms * 1e3, "density": K_TOTAL / nk,
                   "csp_attn_us": csp_ms * 1e3, "csp_attn_tflops": csp_flops / csp_ms / 1e9,
                   "csp_attn_workload": f"{csp_top} scattered + {csp_band} consecutive keys per {csp_bm}-row group"},

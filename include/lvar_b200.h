@@ -56,6 +56,10 @@ typedef struct lvar_attn_args {
    *   M = max_j(s_ij * scale) * log2(e),  L = sum_j exp2(s_ij * scale * log2e - M)  */
   float* M;
   float* L;
+  /* lvar_dense_colsum_attn only: column sums per 128-row query tile, fp32 [B,H,ceil(Lq/128),Lkv], strides in
+   * elements (innermost 1) */
+  float* cs;
+  int64_t cs_sb, cs_sh, cs_st;
   /* block-sparse only: uint8 mask [*, *, ceil(Lq/bs), ceil(Lkv/bs)], nonzero = attend, bs = block_size.
    * A stride of 0 broadcasts over batch / head. Innermost stride is 1. */
   const uint8_t* block_mask;
@@ -87,6 +91,16 @@ typedef struct lvar_attn_args {
  * sattn_triton.dense_attn (kernels/sparse_attn/triton/attn_dense.py:186-231), called from
  * kernels/sparse_attn/sparse_attn_ops.py:21-59 and models/sparvar/basic_sparvar.py:384. */
 int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream);
+
+/* Dense attention and, in the same launch, the exact attention column sums of every 128-row query tile:
+ * cs[b,h,t,j] = sum over the rows i of tile t of softmax(q k^T * scale)[i,j].  After a work item's attention
+ * sweep the kernel holds the final row statistics, keeps the two Q tiles in shared memory, streams the K tiles
+ * a second time and takes the TRANSPOSED product K Q^T, so that a thread owns a key column and sums its 128
+ * probabilities in registers (fixed order, bit-reproducible).  Sums over larger query groups (multiples of
+ * 128 rows) are sums of adjacent tiles.  Replaces dense_colsum_attn_q / _s (dense attention followed by a
+ * separate column-sum kernel, kernels/sparse_attn/sparse_attn_ops.py:65-149,
+ * kernels/sparse_attn/triton/attn_dense_colsum.py:101-296) when the group size is a multiple of 128. */
+int lvar_dense_colsum_attn(const lvar_attn_args* args, lvar_stream_t stream);
 
 /* Block-sparse attention under a 128x128 block mask; rows whose blocks are all masked give 0.
  * Replaces flex_attention(q, k, v, block_mask=...) in SparseFlexAttn.forward

@@ -43,6 +43,7 @@ class AttnArgs(C.Structure):
         ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_sl", C.c_int64),
         ("o", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sl", C.c_int64),
         ("M", C.c_void_p), ("L", C.c_void_p),
+        ("cs", C.c_void_p), ("cs_sb", C.c_int64), ("cs_sh", C.c_int64), ("cs_st", C.c_int64),
         ("block_mask", C.c_void_p), ("bm_sb", C.c_int64), ("bm_sh", C.c_int64), ("bm_sq", C.c_int64),
         ("block_size", C.c_int32),
         ("indices", C.c_void_p), ("i_sb", C.c_int64), ("i_sh", C.c_int64), ("i_sg", C.c_int64),
@@ -59,6 +60,7 @@ class AttnArgs(C.Structure):
 # name -> (restype, argtypes); every symbol the header declares is listed here and checked at load.
 _SIGNATURES = {
     "lvar_dense_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "lvar_dense_colsum_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_block_sparse_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_csp_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_colsum": (C.c_int, [C.c_void_p] * 5 + [C.c_int32] * 5 + [C.c_int64] * 9 + [C.c_int32, C.c_float,

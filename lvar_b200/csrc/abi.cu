@@ -151,6 +151,10 @@ int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream) {
   return lvar::launch_attention(args, 0, static_cast<cudaStream_t>(stream));
 }
 
+int lvar_dense_colsum_attn(const lvar_attn_args* args, lvar_stream_t stream) {
+  return lvar::launch_attention(args, 3, static_cast<cudaStream_t>(stream));
+}
+
 int lvar_block_sparse_attn(const lvar_attn_args* args, lvar_stream_t stream) {
   return lvar::launch_attention(args, 1, static_cast<cudaStream_t>(stream));
 }

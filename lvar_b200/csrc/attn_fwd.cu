@@ -41,11 +41,17 @@ constexpr int kRegsSoftmax = 208, kRegsOther = 72;
 constexpr int kMaxSteps = 1024;  // per-slot KV tile list capacity (block-sparse: Lkv <= 131072)
 constexpr int kStages = 2;
 constexpr int kSchedStages = 2;
+// TMEM buffers per slot for S^T in the column-sum sweep: 1 (S_s) or 2 (S_s and the O region).  Two buffers let
+// the MMA of the next tile run under the softmax warps' reads and measured 6 % slower, like every other
+// change that keeps the tensor pipe busy while TMEM is being read.
+constexpr int kCsBufs = 1;
 // Log2 units by which a row maximum may exceed the row's reference maximum before the reference moves
 // (and O is rescaled).  bf16 has the exponent range of fp32, so P = exp2(s - reference) <= 2^32 is safe.
 constexpr float kRescaleThreshold = 32.0f;
 
-enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2 };
+// MODE_DENSE_CS: dense attention followed, per work item, by a second sweep over the K tiles that takes
+// the attention column sums of the item's two query tiles (see the softmax warps).
+enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2, MODE_DENSE_CS = 3 };
 
 struct AttnParams {
   int B, H, Lq, Lkv, mode;
@@ -55,6 +61,8 @@ struct AttnParams {
   int64_t o_sb, o_sh, o_sl;
   float* M;  // [B,H,Lq] or nullptr
   float* L;  // [B,H,Lq] or nullptr
+  float* cs;  // MODE_DENSE_CS: column sums per 128-row query tile [B,H,ceil(Lq/128),Lkv]
+  int64_t cs_sb, cs_sh, cs_st;
   // block mask (MODE_BLOCK): uint8 [*,*,nqb,nkb], broadcast over batch/head when the stride is 0
   const uint8_t* mask;
   int64_t m_sb, m_sh, m_sq;
@@ -93,9 +101,10 @@ struct Smem {
   static constexpr int kV = kK + kStages * kTile;
   static constexpr int kAux = kV + kStages * kTile;
   // aux: barriers then scalars then the step list
-  static constexpr int kBarBytes = 256;
+  static constexpr int kBarBytes = 512;
   static constexpr int kList = kAux + kBarBytes;
-  static constexpr int kTotal = kList + kSchedStages * 2 * kMaxSteps * 2;  // [stage][slot][kMaxSteps] uint16
+  static constexpr int kNegC = kList + kSchedStages * 2 * kMaxSteps * 2;    // [slot][128] fp32: -(M_i + log2 L_i)
+  static constexpr int kTotal = kNegC + 2 * 128 * 4;
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -121,11 +130,13 @@ struct Bars {
   uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
   uint64_t sched_full[kSchedStages], sched_empty[kSchedStages];
   uint64_t mma_done;
+  // column-sum sweep (MODE_DENSE_CS): S^T of a slot is double-buffered, [slot][buffer]
+  uint64_t cs_full[2][2], cs_empty[2][2];
   SchedEntry sched[kSchedStages];
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(Bars) <= 256, "barrier block too large");
+static_assert(sizeof(Bars) <= 512, "barrier block too large");
 
 }  // namespace
 
@@ -144,6 +155,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Bars* bars = reinterpret_cast<Bars*>(smem + SM::kAux);
   uint16_t* lists = reinterpret_cast<uint16_t*>(smem + SM::kList);  // [kSchedStages][kMaxSteps]
+  float* negc = reinterpret_cast<float*>(smem + SM::kNegC);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -164,6 +176,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&bars->p_full[s], 128);
       mbar_init(&bars->o_full[s], 1);
       mbar_init(&bars->o_empty[s], 128);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&bars->cs_full[s][b], 1);
+        mbar_init(&bars->cs_empty[s][b], 128);
+      }
     }
     for (int i = 0; i < kSchedStages; ++i) {
       mbar_init(&bars->sched_full[i], 1);
@@ -249,6 +265,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     return true;
   };
 
+  // the 128 threads of softmax warpgroup s meet at named barrier 1 + s
+  auto wg_sync = [](int s) {
+    if (s == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+  };
   uint8_t* sQ = smem + SM::kQ;
   uint8_t* sK = smem + SM::kK;
   uint8_t* sV = smem + SM::kV;
@@ -264,6 +285,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t tO = tmem_base + lane_off + TM_O + (uint32_t)s * D;
     int n_s = 0;  // S tiles consumed by this slot so far (parity of s_full)
     int n_o = 0;  // items in which this slot produced an output (parity of o_full)
+    int n_cs[2] = {0, 0};  // column-sum sweep: S^T tiles read per buffer (parity of cs_full)
     bool ok = true;
 
     for (int n = 0; ok; ++n) {
@@ -425,6 +447,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (p.M) p.M[si] = m_true;
         if (p.L) p.L[si] = (it > 0 && l > 0.f) ? l * fast_exp2(m_ref - m_true) : 0.f;
       }
+      if (MODE == MODE_DENSE_CS && n_mine > 0) {
+        // ---- second sweep: column sums of this slot's query tile.  S^T = K Q^T lands in S_s with one KEY per
+        // TMEM lane, so this thread owns key column j*128 + r_in_tile and sums the 128 probabilities
+        // p_i = exp2(s_i * scale - (M_i + log2 L_i)) of the tile's queries in registers.
+        negc[s * 128 + r_in_tile] = (row_ok && l > 0.f) ? -(m_ref + log2f(l)) : -INFINITY;
+        wg_sync(s);  // the warpgroup's 128 constants are in place
+        const float4* nc4 = reinterpret_cast<const float4*>(negc + s * 128);
+        const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+        const int tile = im.row0[s] >> 7;
+        float* cs_row = p.cs + im.b * p.cs_sb + im.h * p.cs_sh + (int64_t)tile * p.cs_st;
+        for (int j = 0; j < n_mine; ++j) {
+          // tile j of the sweep sits in buffer j % kCsBufs: S_s, or the (by now written out) O region
+          const int buf = j % kCsBufs;
+          ok = __all_sync(0xffffffffu, mbar_wait(&bars->cs_full[s][buf], n_cs[buf] & 1, wc, DEV_TIMEOUT_SOFTMAX));
+          if (!ok) break;
+          ++n_cs[buf];
+          tc_fence_after();
+          const uint32_t tT = buf == 0 ? tS : tmem_base + lane_off + TM_O + (uint32_t)s * 128u;
+          float acc = 0.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_x32(tT + c * 32, r);
+            tmem_wait_ld();
+            uint64_t a = 0ull, bsum = 0ull;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 nc = nc4[c * 8 + i];
+              const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])), sc2,
+                                        pack_f32x2(nc.x, nc.y));
+              const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), sc2,
+                                        pack_f32x2(nc.z, nc.w));
+              float x0, x1, y0, y1;
+              unpack_f32x2(t0, x0, x1);
+              unpack_f32x2(t1, y0, y1);
+              a = fadd2(a, pack_f32x2(fast_exp2(x0), fast_exp2(x1)));
+              bsum = fadd2(bsum, pack_f32x2(fast_exp2(y0), fast_exp2(y1)));
+            }
+            float a0, a1, b0, b1;
+            unpack_f32x2(a, a0, a1);
+            unpack_f32x2(bsum, b0, b1);
+            acc += (a0 + a1) + (b0 + b1);
+          }
+          // S^T has been read: the MMA warp may overwrite the buffer with the tile after the next
+          tc_fence_before();
+          mbar_arrive(&bars->cs_empty[s][buf]);
+          const int key = j * 128 + r_in_tile;
+          if (key < p.Lkv) cs_row[key] = acc;
+        }
+        if (!ok) break;
+        wg_sync(s);  // nobody still reads the constants
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
     }
@@ -460,7 +534,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ++nq_items;
         }
         if (MODE != MODE_CSP) {
-          for (int r = 0; r < rounds && ok; ++r) {
+          // MODE_DENSE_CS streams the K tiles a second time for the column-sum sweep
+          const int sweeps = MODE == MODE_DENSE_CS ? 2 : 1;
+          for (int rr = 0; rr < sweeps * rounds && ok; ++rr) {
+            const int r = rr < rounds ? rr : rr - rounds;
             const Round rd = round_info(l0, l1, e, r);
             for (int s = 0; s < 2; ++s) {
               if (!rd.has[s] || (s == 1 && rd.shared)) continue;
@@ -610,6 +687,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       int nq_items = 0;          // items with steps (parity of q_full)
       int n_p[2] = {0, 0};       // P tiles consumed per slot (parity of p_full)
       int n_o[2] = {0, 0};       // items in which the slot produced an output (parity of o_empty)
+      int n_cst[2][2] = {{0, 0}, {0, 0}};  // column-sum sweep: S^T tiles issued per [slot][buffer]
       for (int n = 0; ok; ++n) {
         SchedEntry e;
         ok = acquire_item(n, e, DEV_TIMEOUT_MMA);
@@ -695,13 +773,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pvs[0] = vs[0]; pvs[1] = vs[1]; pvp[0] = vp[0]; pvp[1] = vp[1];
         }
         if (!ok) break;
-        if (rounds > 0) umma_commit_if(leader, &bars->q_empty);
         for (int s = 0; s < 2; ++s) {
           if (npv[s] > 0) {
             umma_commit_if(leader, &bars->o_full[s]);
             ++n_o[s];
           }
         }
+        if (MODE == MODE_DENSE_CS) {
+          // ---- column-sum sweep: S_s^T = K Q_s^T per KV tile (the operands swap roles, the tiles stay where
+          // they are); a slot's next product waits until its softmax warps have read the previous one.
+          for (int r = 0; r < rounds && ok; ++r) {
+            const Round cur = round_info(l0, l1, e, r);
+            int ks = 0, kp = 0;
+            if (cur.has[0] || cur.has[1]) {
+              ks = kc % kStages;
+              kp = (kc / kStages) & 1;
+              ++kc;
+            }
+            const int buf = r % kCsBufs;
+            bool waited = false;
+            for (int s = 0; s < 2 && ok; ++s) {
+              if (!cur.has[s]) continue;
+              // the buffer is free once the softmax warps have read the tile before the previous one out of it
+              if (n_cst[s][buf] > 0) {
+                ok = mbar_wait(&bars->cs_empty[s][buf], (n_cst[s][buf] - 1) & 1, wc, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+              }
+              if (kCsBufs == 2 && r == 1) {
+                // first use of the second buffer, which lies over the O accumulators (over both slots' when the
+                // head dimension is 64): this item's epilogues must have read them
+                for (int t = 0; t < 2 && ok; ++t)
+                  if (t == s || D == 64) ok = mbar_wait(&bars->o_empty[t], (n_o[t] & 1) ^ 1, wc, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+              }
+              if (!waited) {
+                ok = mbar_wait(&bars->k_full[ks], kp, wc, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+                waited = true;
+              }
+              tc_fence_after();
+              const uint32_t tT = tmem_base + (buf == 0 ? (uint32_t)s * 128u : TM_O + (uint32_t)s * 128u);
+              const uint32_t qb = q_lo + (uint32_t)s * TILE16, ka = k_lo + (uint32_t)ks * TILE16;
+#pragma unroll
+              for (int kq = 0; kq < KSTEPS_QK; ++kq) {
+                const uint32_t koff = (kq >> 2) * 1024 + (kq & 3) * 2;
+                umma_ss_if(leader, tT, ka + koff, DESC_HI, qb + koff, DESC_HI, IDESC_QK, kq > 0 ? 1u : 0u);
+              }
+              umma_commit_if(leader, &bars->cs_full[s][buf]);
+              ++n_cst[s][buf];
+              if (s == 1 || !cur.has[1]) umma_commit_if(leader, &bars->k_empty[ks]);  // last reader of the K stage
+            }
+          }
+          // the next item's attention sweep writes S_s and O_s again: the softmax warps' last reads first
+          for (int s = 0; s < 2 && ok; ++s)
+            for (int b = 0; b < 2 && ok; ++b)
+              if (n_cst[s][b] > 0) ok = mbar_wait(&bars->cs_empty[s][b], (n_cst[s][b] - 1) & 1, wc, DEV_TIMEOUT_MMA);
+          if (!ok) break;
+        }
+        if (rounds > 0) umma_commit_if(leader, &bars->q_empty);
         if (lane == 0) mbar_arrive(&bars->sched_empty[n % kSchedStages]);
       }
       // TMEM must not be freed (nor the CTA retire) while an MMA is still in flight, also on abort.
@@ -841,6 +970,7 @@ int launch_d(int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   switch (mode) {
     case MODE_DENSE: return launch_mode<D, MODE_DENSE>(tq, tk, tv, p, grid, stream);
     case MODE_BLOCK: return launch_mode<D, MODE_BLOCK>(tq, tk, tv, p, grid, stream);
+    case MODE_DENSE_CS: return launch_mode<D, MODE_DENSE_CS>(tq, tk, tv, p, grid, stream);
     default: return launch_mode<D, MODE_CSP>(tq, tk, tv, p, grid, stream);
   }
 }
@@ -874,6 +1004,13 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   p.o_sl = a->o_sl;
   p.M = a->M;
   p.L = a->L;
+  if (mode == MODE_DENSE_CS) {
+    LVAR_REQUIRE(a->cs != nullptr, LVAR_ERR_ARG, "cs (column sums per 128-row query tile) is null");
+    p.cs = a->cs;
+    p.cs_sb = a->cs_sb;
+    p.cs_sh = a->cs_sh;
+    p.cs_st = a->cs_st;
+  }
   p.nkb = (a->Lkv + 127) / 128;
   p.status = a->dev_status;
   p.wait_limit_ns = a->wait_limit_ns;

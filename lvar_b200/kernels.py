@@ -94,6 +94,29 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
     return o, M, L
 
 
+def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=None):
+    """Dense attention plus, in the same launch, the attention column sums of every 128-row query tile:
+    returns (o, cs128) with cs128 fp32 [B,H,ceil(Lq/128),Lkv] (and M, L with return_stats)."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(n, t)
+    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    B, H, Lq, _ = q.shape
+    Lkv = k.shape[2]
+    cs = torch.empty((B, H, (Lq + 127) // 128, Lkv), dtype=torch.float32, device=q.device)
+    a = AttnArgs()
+    _fill_qkv(a, q, k, v, o, scale)
+    a.cs, a.cs_sb, a.cs_sh, a.cs_st = cs.data_ptr(), cs.stride(0), cs.stride(1), cs.stride(2)
+    M = L = None
+    if return_stats:
+        M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        L = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        a.M, a.L = M.data_ptr(), L.data_ptr()
+    if status is not None:
+        a.dev_status = status.data_ptr()
+    check(lib.lvar_dense_colsum_attn(C.byref(a), _stream_ptr(q.device)))
+    return (o, cs, M, L) if return_stats else (o, cs)
+
+
 def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None, block=128):
     """Attention under a block mask of 128x128 (or 64x64) blocks: uint8/bool [nq,nk], [H,nq,nk] or [B,H,nq,nk]."""
     for n, t in (("q", q), ("k", k), ("v", v)):

@@ -35,8 +35,24 @@ def dense_attn(q, k, v, scale=None):
 
 def _dense_colsum(q, k, v, scale):
     pad_to = get_kernel_config_attn()["bm"]
-    o, M, L = K.dense_attn_fwd(q, k, v, scale)
-    cs = K.colsum_fwd(q, k, M, L, pad_to, scale)
+    if pad_to % 128 == 0:
+        # one launch: the attention kernel sweeps the K tiles a second time for the column sums of its 128-row
+        # query tiles; a group of pad_to rows is pad_to / 128 adjacent tiles, added in a fixed order
+        o, cs128 = K.dense_colsum_attn_fwd(q, k, v, scale)
+        per = pad_to // 128
+        if per == 1:
+            cs = cs128
+        else:
+            B, H, T, Lkv = cs128.shape
+            G = (T + per - 1) // per
+            if T != G * per:
+                cs128 = torch.nn.functional.pad(cs128, (0, 0, 0, G * per - T))
+            cs = cs128.view(B, H, G, per, Lkv)[:, :, :, 0]
+            for i in range(1, per):
+                cs = cs + cs128.view(B, H, G, per, Lkv)[:, :, :, i]
+    else:
+        o, M, L = K.dense_attn_fwd(q, k, v, scale)
+        cs = K.colsum_fwd(q, k, M, L, pad_to, scale)
     assert o.shape == q.shape, "Output shape mismatch - o: {}, q: {}".format(o.shape, q.shape)
     assert cs.shape == (q.shape[0], q.shape[1], (q.shape[-2] + pad_to - 1) // pad_to, k.shape[2]), \
         "CS shape mismatch - cs: {}, q: {}".format(cs.shape, q.shape)
@@ -46,8 +62,9 @@ def _dense_colsum(q, k, v, scale):
 def dense_colsum_attn_s(q, k, v, scale=None):
     """Dense attention plus exact attention column sums, ``(o, cs)`` with ``cs`` fp32
     [B, H, ceil(Lq/bm), Lkv] (sparse_attn_ops.py:65-113).  The reference's "speed" and "quality"
-    variants differ only in which of its kernels they combine; here both are the same exact pair
-    of passes: attention with row statistics, then a QK^T-only column-sum sweep."""
+    variants differ only in which of its kernels they combine; here both are the same exact two
+    sweeps inside one launch: attention with row statistics, then a K Q^T-only column-sum sweep over the
+    same resident Q tiles (a separate column-sum kernel serves group sizes that are not multiples of 128)."""
     return _dense_colsum(q, k, v, scale)
 
 

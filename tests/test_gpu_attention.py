@@ -241,6 +241,29 @@ def test_csp_attn_all_keys_equals_dense(K):
     assert (o.float() - dense.float()).abs().max().item() <= 8e-3
 
 
+@pytest.mark.parametrize("B,H,Lq,Lkv,D", [(1, 2, 700, 900, 64), (2, 3, 1000, 1300, 128), (1, 1, 100, 77, 128)])
+def test_fused_dense_colsum_matches_separate_kernels_and_oracle(K, B, H, Lq, Lkv, D):
+    """One launch for attention and the column sums of its 128-row query tiles: the output is the dense kernel's
+    bit for bit, the sums agree with the stand-alone column-sum kernel and with the fp64 oracle, ragged tiles
+    and the single-tile tail items included."""
+    from oracle import attention as oa
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    st = K.new_status("cuda")
+    o, cs, M, L = K.dense_colsum_attn_fwd(qc, kc, vc, return_stats=True, status=st)
+    _ok_status(K, st)
+    dense, M0, L0 = K.dense_attn_fwd(qc, kc, vc)
+    assert torch.equal(o, dense) and torch.equal(M, M0) and torch.equal(L, L0)
+    sep = K.colsum_fwd(qc, kc, M0, L0, 128)
+    assert cs.shape == sep.shape == (B, H, (Lq + 127) // 128, Lkv)
+    assert ((cs - sep).abs() <= 1e-5 * sep.abs().max()).all()
+    _, ref = oa.dense_colsum_attn(q, k, v, None, q_group_size=128, dtype=torch.float64)
+    assert ((cs.cpu().double() - ref.double()).abs().max() / ref.double().abs().max()).item() <= CS_REL
+    # twice in a row on the same stream: the work counter and every barrier phase start over cleanly
+    o2, cs2 = K.dense_colsum_attn_fwd(qc, kc, vc)
+    assert torch.equal(o2, o) and torch.equal(cs2, cs)
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_csp_attn_lists_with_runs_of_consecutive_keys(K, D):
     """Tiles of 128 consecutive keys (the local band of a CS4A list) take the tile-copy path, the other tiles
