@@ -7,11 +7,12 @@
 namespace lvar {
 
 // Column-sparse attention gathers the 128 rows of KV tile `j` of an index list into a swizzled [128][D]
-// tile with 16-byte cp.async copies, one warp per tile.  Lane l copies rows l, l+32, l+64 and l+96 whole:
-// it reads its four indices (coalesced across the warp; gather_rows_of_tile, which the loaders call one
-// tile ahead so that the index latency is off the critical path), forms the four row pointers once, and
-// then issues nothing but copies (gather_tile); the 16-byte chunks of a row are consecutive cp.async of
-// the same lane and meet again in L1.  List positions past `cnt` read row 0 (their P columns are zero).
+// tile with 16-byte cp.async copies, one warp per tile.  The tile's 128 indices are read first, coalesced
+// (lane l holds those of rows l, l+32, l+64, l+96; gather_rows_of_tile, which the loaders call one tile ahead
+// so that the index latency is off the critical path).  gather_tile then copies 8 rows per instruction:
+// four lanes share a row (its index comes by shuffle, one row pointer per pass) and copy adjacent chunks
+// of it, which keeps both the number of cache lines per instruction (8) and the address arithmetic per
+// copy low.  List positions past `cnt` read row 0 (their P columns are zero).
 __device__ __forceinline__ void gather_rows_of_tile(int (&kv)[4], const int32_t* idx, int cnt, int j, int Lkv,
                                                     int lane, int* status) {
 #pragma unroll
@@ -37,15 +38,23 @@ __device__ __forceinline__ bool tile_is_run(const int (&kv)[4], int cnt, int j, 
 template <int D>
 __device__ __forceinline__ void gather_tile(uint32_t dst, const __nv_bfloat16* base, int64_t row_stride,
                                             const int (&kv)[4], int lane) {
-  constexpr int CH = D / 8;  // 16-byte chunks per row
-  const uint32_t x = (uint32_t)(lane & 7);  // rows l + 32 i all have r % 8 == l % 8: one swizzle pattern per lane
+  constexpr int CH = D / 8;      // 16-byte chunks per row
+  constexpr int RPI = 8;         // rows per instruction (measured: 8 beats 2, 4, 16 and 32)
+  constexpr int LPR = 32 / RPI;  // lanes that share a row
+  constexpr int CPL = CH / LPR;  // chunks per lane and row
+  const int g = lane / LPR, cq = lane % LPR;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat16* src = base + (int64_t)kv[i] * row_stride;
-    const uint32_t drow = dst + (uint32_t)(i * 32 + lane) * 128u;
+  for (int pass = 0; pass < 128 / RPI; ++pass) {
+    const int r = pass * RPI + g;
+    const int row = __shfl_sync(0xffffffffu, kv[(pass * RPI) >> 5], r & 31);
+    const __nv_bfloat16* src = base + (int64_t)row * row_stride;
+    const uint32_t drow = dst + (uint32_t)r * 128u;
+    const uint32_t x = (uint32_t)(r & 7);
 #pragma unroll
-    for (int c = 0; c < CH; ++c)
+    for (int i = 0; i < CPL; ++i) {
+      const int c = i * LPR + cq;
       cp_async_16_l1(drow + (uint32_t)(c >> 3) * 16384u + ((((uint32_t)c & 7u) ^ x) << 4), src + c * 8);
+    }
   }
 }
 
