@@ -888,16 +888,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             return bits;
           };
           const int qt0 = im.row0[0] >> 7, qt1 = im.row0[1] >> 7;
-          for (int base = 0; base < p.nkb; base += 32) {
-            const int j = base + lane;
-            const uint32_t b0 = (j < p.nkb && (im.live & 1u)) ? sub_bits(qt0, j) : 0u;
-            const uint32_t b1 = (j < p.nkb && (im.live & 2u)) ? sub_bits(qt1, j) : 0u;
-            const uint32_t v0 = __ballot_sync(0xffffffffu, b0 != 0), v1 = __ballot_sync(0xffffffffu, b1 != 0);
-            const int p0 = n0 + __popc(v0 & lt), p1 = n1 + __popc(v1 & lt);
-            if (b0 && p0 < kMaxSteps) l0[p0] = (uint16_t)(j | (b0 << 12));
-            if (b1 && p1 < kMaxSteps) l1[p1] = (uint16_t)(j | (b1 << 12));
-            n0 += __popc(v0);
-            n1 += __popc(v1);
+          // Tiles that both slots want come first, in the same positions of both lists, so that they are
+          // loaded once (a round shares a tile when both lists name it at the same position); the tiles
+          // only one slot wants follow.  Ascending within each class.
+          for (int pass = 0; pass < 2; ++pass) {
+            for (int base = 0; base < p.nkb; base += 32) {
+              const int j = base + lane;
+              uint32_t b0 = (j < p.nkb && (im.live & 1u)) ? sub_bits(qt0, j) : 0u;
+              uint32_t b1 = (j < p.nkb && (im.live & 2u)) ? sub_bits(qt1, j) : 0u;
+              const bool both = b0 != 0 && b1 != 0;
+              if (both != (pass == 0)) b0 = b1 = 0u;
+              const uint32_t v0 = __ballot_sync(0xffffffffu, b0 != 0), v1 = __ballot_sync(0xffffffffu, b1 != 0);
+              const int p0 = n0 + __popc(v0 & lt), p1 = n1 + __popc(v1 & lt);
+              if (b0 && p0 < kMaxSteps) l0[p0] = (uint16_t)(j | (b0 << 12));
+              if (b1 && p1 < kMaxSteps) l1[p1] = (uint16_t)(j | (b1 << 12));
+              n0 += __popc(v0);
+              n1 += __popc(v1);
+            }
           }
           n0 = min(n0, kMaxSteps);
           n1 = min(n1, kMaxSteps);
