@@ -74,6 +74,11 @@ typedef struct lvar_attn_args {
   const void* o_in;   /* bf16 [B,H,Lq,D] accumulate input; may be the same buffer as o */
   int64_t oi_sb, oi_sh, oi_sl;
   int32_t o_scale; /* +1 or -1 */
+  /* o_in_side > 0: o_in is instead a cache [B,H,o_in_side^2,D] over a square token grid, and the accumulate
+   * input of query row y * o_side + x (o_side^2 == Lq) is its bilinear resize to the o_side grid
+   * (align_corners = False, fp32 interpolation rounded to bf16 once), bit-identical to lvar_upsample_ocache
+   * followed by a plain accumulate; o_in must then not be the output buffer.  0: o_in is [B,H,Lq,D]. */
+  int32_t o_in_side, o_side;
   /* scheduling: the kernels are persistent (one CTA per SM) and draw work items from a counter in
    * device memory.  sched_scratch points to TWO int32 that are zero when the kernel starts; the kernel
    * leaves them zero, so one zeroed buffer serves every later launch on the same stream.  Launches
@@ -112,7 +117,8 @@ int lvar_block_sparse_attn(const lvar_attn_args* args, lvar_stream_t stream);
  * Replaces torch.ops.chipmunk.csp_attn (kernels/chipmunk/csrc/attn/csp_attn.cu:318-433) and
  * sattn_triton.csp_attn (kernels/sparse_attn/triton/attn_csp.py:215-265), called from
  * kernels/sparse_attn/sparse_attn_ops.py:273-292. Unlike the reference, counts need not be a
- * multiple of the KV tile. */
+ * multiple of the KV tile.  With o_in_side > 0 the launch also takes over the O-cache resize that
+ * precedes it in a sparse step (upsample_Ocache, models/sparvar/sparse_attn.py:324-362). */
 int lvar_csp_attn(const lvar_attn_args* args, lvar_stream_t stream);
 
 /* Attention column sums (KV-importance scores) given the row statistics of a previous attention pass:

@@ -50,7 +50,7 @@ class AttnArgs(C.Structure):
         ("counts", C.c_void_p), ("c_sb", C.c_int64), ("c_sh", C.c_int64),
         ("group_rows", C.c_int32),
         ("o_in", C.c_void_p), ("oi_sb", C.c_int64), ("oi_sh", C.c_int64), ("oi_sl", C.c_int64),
-        ("o_scale", C.c_int32),
+        ("o_scale", C.c_int32), ("o_in_side", C.c_int32), ("o_side", C.c_int32),
         ("sched_scratch", C.c_void_p), ("work_order", C.c_void_p),
         ("dev_status", C.c_void_p),
         ("wait_limit_ns", C.c_uint64),

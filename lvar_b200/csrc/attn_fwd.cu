@@ -82,6 +82,9 @@ struct AttnParams {
   const __nv_bfloat16* o_in;  // accumulate input (may alias o)
   int64_t oi_sb, oi_sh, oi_sl;
   float o_scale;
+  int oi_side;      // > 0: o_in is a cache over an oi_side x oi_side token grid, resized on the fly
+  int o_side;       // side of the query grid (o_side^2 == Lq) when oi_side > 0
+  float oi_ratio;   // oi_side / o_side
   // persistent scheduling
   int n_x;            // query-tile pairs per (batch, head)
   int n_pair_items;   // items [0, n_pair_items) are pairs, [n_pair_items, total_items) single tiles
@@ -401,6 +404,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
       const __nv_bfloat16* irow =
           (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
+      // accumulate input taken from a coarser token grid: this row's four source tokens and weights
+      const bool resize = (MODE == MODE_CSP) && p.oi_side > 0;
+      BilinearTaps tp = {};
+      const __nv_bfloat16* ibase = nullptr;
+      if (resize && row_ok) {
+        tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
+        ibase = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
+      }
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -429,7 +440,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (MODE == MODE_CSP) {
               // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
               // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
-              const uint4 prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
+              uint4 prev;
+              if (resize) {
+                const __nv_bfloat16* ib = ibase + c * 32 + q4 * 8;
+                prev = bilinear_mix8(tp, *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r00 * p.oi_sl),
+                                     *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r01 * p.oi_sl),
+                                     *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r10 * p.oi_sl),
+                                     *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r11 * p.oi_sl));
+              } else {
+                prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
+              }
               const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -1071,6 +1091,15 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     p.oi_sh = a->oi_sh;
     p.oi_sl = a->oi_sl;
     p.o_scale = (float)a->o_scale;
+    p.oi_side = 0;
+    if (a->o_in_side > 0) {
+      LVAR_REQUIRE(a->o_side >= 1 && (int64_t)a->o_side * a->o_side == a->Lq, LVAR_ERR_ARG,
+                   "o_in_side > 0 needs a square query grid: o_side * o_side must equal Lq");
+      LVAR_REQUIRE(a->o_in != a->o, LVAR_ERR_ARG, "a resized o_in cannot be the output buffer");
+      p.oi_side = a->o_in_side;
+      p.o_side = a->o_side;
+      p.oi_ratio = (float)a->o_in_side / (float)a->o_side;
+    }
     const int groups = (a->Lq + a->group_rows - 1) / a->group_rows;
     p.n_x = groups * p.chunks_per_group;
   } else {

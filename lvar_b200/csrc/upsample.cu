@@ -21,37 +21,14 @@ __global__ void upsample_ocache_kernel(const __nv_bfloat16* __restrict__ src, __
     const int x = (int)(pix % t);
     const int y = (int)((pix / t) % t);
     const int64_t bh = pix / ((int64_t)t * t);
-    // source index: ratio * (dst + 0.5) - 0.5, clamped at 0
-    const float fy = fmaxf(ratio * (y + 0.5f) - 0.5f, 0.f);
-    const float fx = fmaxf(ratio * (x + 0.5f) - 0.5f, 0.f);
-    const int y0 = min((int)fy, s - 1), x0 = min((int)fx, s - 1);
-    const int y1 = min(y0 + 1, s - 1), x1 = min(x0 + 1, s - 1);
-    const float ly = fy - (float)y0, lx = fx - (float)x0;
-    const float hy = 1.f - ly, hx = 1.f - lx;
+    const BilinearTaps tp = bilinear_taps(y, x, s, ratio);
     const __nv_bfloat16* base = src + bh * src_bh_stride + c * 8;
-    const uint4 a = *reinterpret_cast<const uint4*>(base + (int64_t)(y0 * s + x0) * src_row_stride);
-    const uint4 b = *reinterpret_cast<const uint4*>(base + (int64_t)(y0 * s + x1) * src_row_stride);
-    const uint4 cc = *reinterpret_cast<const uint4*>(base + (int64_t)(y1 * s + x0) * src_row_stride);
-    const uint4 d = *reinterpret_cast<const uint4*>(base + (int64_t)(y1 * s + x1) * src_row_stride);
-    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
-    const uint32_t cv[4] = {cc.x, cc.y, cc.z, cc.w}, dv[4] = {d.x, d.y, d.z, d.w};
-    uint32_t out[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float r[2];
-#pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        const float va = __uint_as_float(hlf ? (av[j] & 0xffff0000u) : (av[j] << 16));
-        const float vb = __uint_as_float(hlf ? (bv[j] & 0xffff0000u) : (bv[j] << 16));
-        const float vc = __uint_as_float(hlf ? (cv[j] & 0xffff0000u) : (cv[j] << 16));
-        const float vd = __uint_as_float(hlf ? (dv[j] & 0xffff0000u) : (dv[j] << 16));
-        r[hlf] = hy * (hx * va + lx * vb) + ly * (hx * vc + lx * vd);
-      }
-      const __nv_bfloat162 pk = __floats2bfloat162_rn(r[0], r[1]);
-      out[j] = *reinterpret_cast<const uint32_t*>(&pk);
-    }
+    const uint4 a = *reinterpret_cast<const uint4*>(base + (int64_t)tp.r00 * src_row_stride);
+    const uint4 b = *reinterpret_cast<const uint4*>(base + (int64_t)tp.r01 * src_row_stride);
+    const uint4 cc = *reinterpret_cast<const uint4*>(base + (int64_t)tp.r10 * src_row_stride);
+    const uint4 d = *reinterpret_cast<const uint4*>(base + (int64_t)tp.r11 * src_row_stride);
     *reinterpret_cast<uint4*>(dst + bh * dst_bh_stride + (int64_t)(y * t + x) * dst_row_stride + c * 8) =
-        make_uint4(out[0], out[1], out[2], out[3]);
+        bilinear_mix8(tp, a, b, cc, d);
   }
 }
 

@@ -6,6 +6,7 @@ launches on the current CUDA stream and returns without synchronising.  Nothing 
 from __future__ import annotations
 
 import ctypes as C
+import math
 from typing import Optional, Tuple
 
 import torch
@@ -157,8 +158,12 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
     return (o, M, L) if return_stats else o
 
 
-def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None, *, out=None, status=None):
-    """out = o_in + o_scale * softmax(q k[idx]^T * scale) v[idx] per query group of `group_rows` rows."""
+def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None, *, out=None, status=None,
+                 resize_from: int = 0):
+    """out = o_in + o_scale * softmax(q k[idx]^T * scale) v[idx] per query group of `group_rows` rows.
+
+    ``resize_from`` = s > 0: ``o_in`` is a cache [B,H,s*s,D] over a square token grid and is resized bilinearly
+    to the (square) query grid inside the same launch, with the bits of ``upsample_ocache`` + a plain call."""
     for n, t in (("q", q), ("k", k), ("v", v), ("o", o_in)):
         _require_cuda_bf16(n, t)
     B, H, Lq, _ = q.shape
@@ -170,11 +175,20 @@ def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None
                            f"[B={B}, H={H}, G={G}, *]")
     if indices.stride(-1) != 1 or counts.stride(-1) != 1:
         raise RuntimeError("indices and counts must have a contiguous last dimension")
-    if o_in.shape != q.shape:
+    side = 0
+    if resize_from:
+        side = math.isqrt(Lq)
+        if side * side != Lq:
+            raise RuntimeError(f"resize_from needs a square query grid, Lq = {Lq}")
+        want = (B, H, resize_from * resize_from, q.shape[3])
+        if tuple(o_in.shape) != want:
+            raise RuntimeError(f"Cache shape mismatch - o_in: {tuple(o_in.shape)}, expected {want}")
+    elif o_in.shape != q.shape:
         raise RuntimeError("Output shape mismatch - o: {}, q: {}".format(tuple(o_in.shape), tuple(q.shape)))
     o = torch.empty_like(q, memory_format=torch.contiguous_format) if out is None else out
     a = AttnArgs()
     _fill_qkv(a, q, k, v, o, scale)
+    a.o_in_side, a.o_side = int(resize_from), side
     a.indices = indices.data_ptr()
     a.i_sb, a.i_sh, a.i_sg = indices.stride(0), indices.stride(1), indices.stride(2)
     a.counts = counts.data_ptr()

@@ -257,7 +257,7 @@ class SparseDiffAttn:
         return o
 
     def _sparse_step(self, q, k, v, scale, scale_ind):
-        from .sparse_attn_ops import csp_attn
+        from .sparse_attn_ops import csp_attn, csp_attn_resized
         st = self.storage
         assert st.indices is not None, "sparse step before the decision (full) step of this layer"
         B, H, q_len, _ = q.shape
@@ -273,11 +273,9 @@ class SparseDiffAttn:
         if scale_ind != len(self.scales) - 1:
             st.indices, st.counts, st.count_value = lists, counts, total
         if self.use_o_cache:
-            cache = st.out_cache[:B]
-            o = K.upsample_ocache(cache.to(v.dtype), cache.shape[-2], q_len)
-        else:
-            o = torch.zeros_like(q)
-        return csp_attn(q, k, v, scale, lists, counts, o, 1)
+            # the cache is resized to this scale's grid inside the attention launch
+            return csp_attn_resized(q, k, v, scale, lists, counts, st.out_cache[:B].to(v.dtype), 1)
+        return csp_attn(q, k, v, scale, lists, counts, torch.zeros_like(q), 1)
 
     def forward(self, q, k, v, scale, do_full_step: bool = False, inference_step: int = 0, scale_ind: int = 0,
                 layer_ind: int = 0):

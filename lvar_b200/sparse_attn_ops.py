@@ -16,7 +16,7 @@ from . import kernels as K
 from .sparse_attn_config import GLOBAL_CONFIG, get_kernel_config_attn
 
 __all__ = [
-    "dense_attn", "dense_colsum_attn_s", "dense_colsum_attn_q", "naive_dense_colsum_attn", "csp_attn",
+    "dense_attn", "dense_colsum_attn_s", "dense_colsum_attn_q", "naive_dense_colsum_attn", "csp_attn", "csp_attn_resized",
     "block_sparse_attn", "bitpack", "bitunpack", "copy_indices", "topk_indices", "scatter_add", "mask_to_indices",
 ]
 
@@ -102,6 +102,21 @@ def csp_attn(q, k, v, scale, indices, indices_counts, o, o_scale):
     assert o.shape == q.shape, "Output shape mismatch - o: {}, q: {}".format(o.shape, q.shape)
     bm = get_kernel_config_attn()["bm"]
     return K.csp_attn_fwd(q, k, v, indices, indices_counts, o, int(o_scale), bm, scale)
+
+
+def csp_attn_resized(q, k, v, scale, indices, indices_counts, o_cache, o_scale):
+    """``csp_attn`` whose accumulate input is an O-cache of a coarser square token grid: the bilinear resize
+    the policy does before every sparse step (upsample_Ocache, models/sparvar/sparse_attn.py:324-362) runs in
+    the attention kernel's epilogue instead of as a launch of its own.  Same bits as
+    ``csp_attn(..., upsample_ocache(o_cache, ...), o_scale)``."""
+    assert indices.shape == (q.shape[0], q.shape[1], indices.shape[2], k.shape[-2]), \
+        "Indices shape mismatch - indices: {}, q: {}, k: {}".format(indices.shape, q.shape, k.shape)
+    assert indices_counts.shape == indices.shape[:-1], \
+        "Indices counts shape mismatch - indices_counts: {}, indices: {}".format(indices_counts.shape, indices.shape)
+    side = math.isqrt(o_cache.shape[-2])
+    assert side * side == o_cache.shape[-2], "O-cache is not a square token grid: {}".format(o_cache.shape)
+    bm = get_kernel_config_attn()["bm"]
+    return K.csp_attn_fwd(q, k, v, indices, indices_counts, o_cache, int(o_scale), bm, scale, resize_from=side)
 
 
 def block_sparse_attn(q, k, v, block_mask, scale=None, block_size=128):

@@ -264,6 +264,28 @@ def test_fused_dense_colsum_matches_separate_kernels_and_oracle(K, B, H, Lq, Lkv
     assert torch.equal(o2, o) and torch.equal(cs2, cs)
 
 
+@pytest.mark.parametrize("s_side,t_side,D,bm", [(12, 16, 128, 256), (5, 13, 64, 64), (16, 16, 128, 192), (20, 17, 64, 256)])
+def test_csp_attn_with_resized_ocache_matches_two_launches(K, s_side, t_side, D, bm):
+    """The O-cache resize inside the attention epilogue gives the bits of the stand-alone resize kernel followed
+    by a plain column-sparse call (ragged last query tile, up- and down-sizing, equal grids)."""
+    B, H, Lq, Lkv = 2, 2, t_side * t_side, 500
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=s_side)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    G = (Lq + bm - 1) // bm
+    g = torch.Generator().manual_seed(t_side)
+    idx = torch.randint(0, Lkv, (B, H, G, Lkv), generator=g, dtype=torch.int32).cuda()
+    counts = torch.randint(0, 300, (B, H, G), generator=g, dtype=torch.int32).cuda()
+    cache = torch.randn(B, H, s_side * s_side, D, generator=g).bfloat16().cuda()
+    for o_scale in (1, -1):
+        st = K.new_status("cuda")
+        fused = K.csp_attn_fwd(qc, kc, vc, idx, counts, cache, o_scale, bm, resize_from=s_side, status=st)
+        _ok_status(K, st)
+        two = K.csp_attn_fwd(qc, kc, vc, idx, counts, K.upsample_ocache(cache, s_side * s_side, Lq), o_scale, bm)
+        assert torch.equal(fused, two)
+    with pytest.raises(RuntimeError):
+        K.csp_attn_fwd(qc, kc, vc, idx, counts, cache[:, :, :-1], 1, bm, resize_from=s_side)
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_csp_attn_lists_with_runs_of_consecutive_keys(K, D):
     """Tiles of 128 consecutive keys (the local band of a CS4A list) take the tile-copy path, the other tiles
