@@ -234,6 +234,10 @@ def run_ours(args):
     dense_ms = timed(lambda: K.dense_attn_fwd(q, k, v, scale), 10)
     colsum_ms = timed(lambda: K.colsum_fwd(q, k, M, L, BLOCK, scale), 10)
     fused_ms = timed(lambda: K.dense_colsum_attn_fwd(q, k, v, scale), 10)  # attention + column sums, one launch
+    # column sums without an attention output: statistics sweep + transposed sweep in one launch, and the
+    # transposed sweep alone on the dense kernel's statistics
+    cs_only_ms = timed(lambda: K.colsum_tiles_fwd(q, k, scale), 10)
+    cs_given_ms = timed(lambda: K.colsum_tiles_fwd(q, k, scale, stats=(M, L)), 10)
     mask_ms = timed(lambda: K.build_block_mask(K.block_scores(cs, BLOCK), always, K_TOTAL), 10)
 
     # ---- the column-sparse kernel on a list shaped like a last-scale sparse step: per 256-row query group
@@ -382,6 +386,7 @@ def run_ours(args):
         "clocks": clocks.summary(),
         "extra": {"dense_attn_ms": dense_ms, "dense_attn_tflops": dense_flops / dense_ms / 1e9,
                   "colsum_sweep_us": colsum_ms * 1e3, "dense_colsum_fused_ms": fused_ms,
+                  "colsum_only_us": cs_only_ms * 1e3, "colsum_from_given_stats_us": cs_given_ms * 1e3,
                   "colsum_over_dense_attn": (fused_ms - dense_ms) / dense_ms,
                   "colsum_over_dense_attn_separate_kernels": colsum_ms / dense_ms,
                   "mask_build_us": mask_ms * 1e3, "density": K_TOTAL / nk,

@@ -107,6 +107,15 @@ int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream);
  * kernels/sparse_attn/triton/attn_dense_colsum.py:101-296) when the group size is a multiple of 128. */
 int lvar_dense_colsum_attn(const lvar_attn_args* args, lvar_stream_t stream);
 
+/* The attention column sums alone, per 128-row query tile (cs as in lvar_dense_colsum_attn); v, o and their
+ * strides are not read and may be null / 0.  stats_given = 0: one launch takes the row statistics in a first
+ * sweep that does everything but P and PV (M and L are written when non-null) and the sums in a second one.
+ * stats_given != 0: args->M and args->L are inputs (as lvar_dense_attn writes them) and only the second sweep
+ * runs.  This is the KV-importance score of a scale when no attention output is wanted
+ * (the scores dense_colsum_attn_q / _s return next to o, kernels/sparse_attn/sparse_attn_ops.py:65-149; the
+ * reference has no entry point without the output). */
+int lvar_colsum_tiles(const lvar_attn_args* args, int32_t stats_given, lvar_stream_t stream);
+
 /* Block-sparse attention under a 128x128 block mask; rows whose blocks are all masked give 0.
  * Replaces flex_attention(q, k, v, block_mask=...) in SparseFlexAttn.forward
  * (models/sparvar/basic_sparvar.py:187-194). */

@@ -61,6 +61,7 @@ class AttnArgs(C.Structure):
 _SIGNATURES = {
     "lvar_dense_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_dense_colsum_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "lvar_colsum_tiles": (C.c_int, [C.POINTER(AttnArgs), C.c_int32, C.c_void_p]),
     "lvar_block_sparse_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_csp_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_colsum": (C.c_int, [C.c_void_p] * 5 + [C.c_int32] * 5 + [C.c_int64] * 9 + [C.c_int32, C.c_float,

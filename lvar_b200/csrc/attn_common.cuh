@@ -92,7 +92,6 @@ __device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], uint64_t
   }
 }
 
-
 // exp2 of two values on the FMA pipe (no MUFU): x = j + f with j = round(x), |f| <= 0.5; 2^f by a
 // degree-4 minimax polynomial (relative error 2.7e-6), 2^j by adding j to the exponent field.
 // Valid for -126 <= x <= 100; the caller guarantees the range (no masked, i.e. -inf, inputs).
@@ -114,10 +113,9 @@ __device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& o0, float& o1) 
   o1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
-// Same as exp_pack_chunk with the exponentials evaluated on the FMA pipe; only for tiles without
-// masked columns.  Inputs below 2^-126 are clamped (they contribute ~1e-38 instead of 0).
-__device__ __forceinline__ void exp_pack_chunk_poly(const uint32_t (&r)[32], uint64_t sc2, uint64_t nm2,
-                                                    uint64_t& sum_a, uint64_t& sum_b, uint32_t (&pk)[32], int off) {
+// exp_pack_chunk without the packing: only the row sum of the 32 exponentials is kept.
+__device__ __forceinline__ void exp_sum_chunk(const uint32_t (&r)[32], uint64_t sc2, uint64_t nm2, uint64_t& sum_a,
+                                              uint64_t& sum_b) {
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
     const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
@@ -125,13 +123,42 @@ __device__ __forceinline__ void exp_pack_chunk_poly(const uint32_t (&r)[32], uin
     float a0, a1, b0, b1;
     unpack_f32x2(t0, a0, a1);
     unpack_f32x2(t1, b0, b1);
-    exp2_poly_x2(pack_f32x2(fmaxf(a0, -126.f), fmaxf(a1, -126.f)), a0, a1);
-    exp2_poly_x2(pack_f32x2(fmaxf(b0, -126.f), fmaxf(b1, -126.f)), b0, b1);
-    sum_a = fadd2(sum_a, pack_f32x2(a0, a1));
-    sum_b = fadd2(sum_b, pack_f32x2(b0, b1));
-    pk[off + i / 2] = pack_bf16x2(a0, a1);
-    pk[off + i / 2 + 1] = pack_bf16x2(b0, b1);
+    sum_a = fadd2(sum_a, pack_f32x2(fast_exp2(a0), fast_exp2(a1)));
+    sum_b = fadd2(sum_b, pack_f32x2(fast_exp2(b0), fast_exp2(b1)));
   }
+}
+
+// Sum over 32 queries of exp2(s_i * scale + c_i): one 32-column chunk of a key's S^T row (raw fp32 bits in r),
+// the per-query constants c_i = -(M_i + log2 L_i) read as float4 from shared memory (the same address for the
+// whole warp: a broadcast).
+// Groups of four whose bit is set in POLY take their exponentials from exp2_poly_x2 (inputs clamped at -126).
+template <uint32_t POLY>
+__device__ __forceinline__ float colsum_chunk(const uint32_t (&r)[32], const float4* nc4, uint64_t sc2) {
+  uint64_t a = 0ull, b = 0ull;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 nc = nc4[i];
+    const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])), sc2,
+                              pack_f32x2(nc.x, nc.y));
+    const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), sc2,
+                              pack_f32x2(nc.z, nc.w));
+    float x0, x1, y0, y1;
+    unpack_f32x2(t0, x0, x1);
+    unpack_f32x2(t1, y0, y1);
+    if ((POLY >> i) & 1u) {
+      exp2_poly_x2(pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f)), x0, x1);
+      exp2_poly_x2(pack_f32x2(fmaxf(y0, -126.f), fmaxf(y1, -126.f)), y0, y1);
+      a = fadd2(a, pack_f32x2(x0, x1));
+      b = fadd2(b, pack_f32x2(y0, y1));
+    } else {
+      a = fadd2(a, pack_f32x2(fast_exp2(x0), fast_exp2(x1)));
+      b = fadd2(b, pack_f32x2(fast_exp2(y0), fast_exp2(y1)));
+    }
+  }
+  float a0, a1, b0, b1;
+  unpack_f32x2(a, a0, a1);
+  unpack_f32x2(b, b0, b1);
+  return (a0 + a1) + (b0 + b1);
 }
 
 }  // namespace lvar

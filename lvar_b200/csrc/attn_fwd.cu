@@ -28,6 +28,8 @@
 // CTA-wide abort flag, lets the loaders drain their copies, frees TMEM and returns.
 #include <math.h>
 
+#include <type_traits>
+
 #include "attn_common.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
@@ -45,13 +47,20 @@ constexpr int kSchedStages = 2;
 // the MMA of the next tile run under the softmax warps' reads and measured 6 % slower, like every other
 // change that keeps the tensor pipe busy while TMEM is being read.
 constexpr int kCsBufs = 1;
+// Column-sum sweep: which of the 8 groups of four exponentials per 32-column chunk are evaluated on the FMA
+// pipe (polynomial) instead of the exp2 unit, the sweep's bottleneck.  A quarter of them measured best
+// (0.47 -> 0.42 ms for the sweep at 4096 x 10521 x 32 heads; three eighths or a half: 0.43-0.45 ms); the same
+// mix in the statistics sweep of MODE_CS_ONLY gained nothing and is not used.
+constexpr uint32_t kCsPolyMask = 0x88;
 // Log2 units by which a row maximum may exceed the row's reference maximum before the reference moves
 // (and O is rescaled).  bf16 has the exponent range of fp32, so P = exp2(s - reference) <= 2^32 is safe.
 constexpr float kRescaleThreshold = 32.0f;
 
 // MODE_DENSE_CS: dense attention followed, per work item, by a second sweep over the K tiles that takes
 // the attention column sums of the item's two query tiles (see the softmax warps).
-enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2, MODE_DENSE_CS = 3 };
+// MODE_CS_ONLY: the column sums alone.  The first sweep only takes the row statistics (no P, no PV, no V
+// loads, no output), or is left out when the caller supplies them; the second sweep is MODE_DENSE_CS's.
+enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2, MODE_DENSE_CS = 3, MODE_CS_ONLY = 4 };
 
 struct AttnParams {
   int B, H, Lq, Lkv, mode;
@@ -61,8 +70,10 @@ struct AttnParams {
   int64_t o_sb, o_sh, o_sl;
   float* M;  // [B,H,Lq] or nullptr
   float* L;  // [B,H,Lq] or nullptr
-  float* cs;  // MODE_DENSE_CS: column sums per 128-row query tile [B,H,ceil(Lq/128),Lkv]
+  float* cs;  // MODE_DENSE_CS / MODE_CS_ONLY: column sums per 128-row query tile [B,H,ceil(Lq/128),Lkv]
   int64_t cs_sb, cs_sh, cs_st;
+  const float* M_in;  // MODE_CS_ONLY: row statistics supplied by the caller (both or neither); the
+  const float* L_in;  // statistics sweep is then skipped
   // block mask (MODE_BLOCK): uint8 [*,*,nqb,nkb], broadcast over batch/head when the stride is 0
   const uint8_t* mask;
   int64_t m_sb, m_sh, m_sq;
@@ -153,6 +164,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc_bf16(128, D, 0, 1);
   constexpr uint32_t TM_O = 256;
+  constexpr bool kHasCs = MODE == MODE_DENSE_CS || MODE == MODE_CS_ONLY;  // column-sum sweep after the first one
+  // MODE_CS_ONLY with the caller's row statistics: no first sweep at all
+  const bool stats_given = MODE == MODE_CS_ONLY && p.M_in != nullptr;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -304,7 +318,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
       int it = 0;
-      for (int j = 0; j < n_mine; ++j) {
+      const int n_first = stats_given ? 0 : n_mine;
+      for (int j = 0; j < n_first; ++j) {
         const int kvb = (MODE == MODE_BLOCK) ? (mylist[j] & 0xFFF) : j;
         const uint32_t sub = (MODE == MODE_BLOCK) ? ((uint32_t)mylist[j] >> 12 >> (2 * (r_in_tile >> 6))) & 3u : 3u;
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, wc, DEV_TIMEOUT_SOFTMAX));
@@ -319,6 +334,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_x32(tS + 64, s2);
         tmem_ld_x32(tS + 96, s3);
         tmem_wait_ld();
+        if (MODE == MODE_CS_ONLY) {
+          // nothing goes back into S_s: the next tile's product may land while this one is exponentiated
+          tc_fence_before();
+          mbar_arrive(&bars->p_full[s]);
+        }
 
         const int valid = (MODE == MODE_CSP) ? (cnt_total - j * 128) : (p.Lkv - kvb * 128);
         if (valid < 128 || sub != 3u) {
@@ -344,7 +364,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             m_ref = mx_s;
           }
           l *= alpha;
-          if (it > 0) {
+          if (MODE != MODE_CS_ONLY && it > 0) {
             const uint64_t a2 = pack_f32x2(alpha, alpha);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -368,17 +388,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;  // row with nothing to attend yet: all p = 0
         const uint64_t nm2 = pack_f32x2(neg_m, neg_m);
         uint64_t sum_a = 0ull, sum_b = 0ull;  // two packed accumulators = four partial row sums
-        {
-          uint32_t pk[32];
-          exp_pack_chunk(s0, sc2, nm2, sum_a, sum_b, pk, 0);
-          exp_pack_chunk(s1, sc2, nm2, sum_a, sum_b, pk, 16);
-          tmem_st_x32(tS, pk);
-        }
-        {
-          uint32_t pk[32];
-          exp_pack_chunk(s2, sc2, nm2, sum_a, sum_b, pk, 0);
-          exp_pack_chunk(s3, sc2, nm2, sum_a, sum_b, pk, 16);
-          tmem_st_x32(tS + 32, pk);
+        if (MODE == MODE_CS_ONLY) {
+          exp_sum_chunk(s0, sc2, nm2, sum_a, sum_b);
+          exp_sum_chunk(s1, sc2, nm2, sum_a, sum_b);
+          exp_sum_chunk(s2, sc2, nm2, sum_a, sum_b);
+          exp_sum_chunk(s3, sc2, nm2, sum_a, sum_b);
+        } else {
+          {
+            uint32_t pk[32];
+            exp_pack_chunk(s0, sc2, nm2, sum_a, sum_b, pk, 0);
+            exp_pack_chunk(s1, sc2, nm2, sum_a, sum_b, pk, 16);
+            tmem_st_x32(tS, pk);
+          }
+          {
+            uint32_t pk[32];
+            exp_pack_chunk(s2, sc2, nm2, sum_a, sum_b, pk, 0);
+            exp_pack_chunk(s3, sc2, nm2, sum_a, sum_b, pk, 16);
+            tmem_st_x32(tS + 32, pk);
+          }
         }
         {
           float a0, a1, b0, b1;
@@ -386,136 +413,138 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           unpack_f32x2(sum_b, b0, b1);
           l += (a0 + a1) + (b0 + b1);
         }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bars->p_full[s]);
+        if (MODE != MODE_CS_ONLY) {
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bars->p_full[s]);
+        }
         ++it;
       }
       if (!ok) break;
 
       // ---- epilogue: O / l -> bf16 -> global; row statistics
-      if (it > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, wc, DEV_TIMEOUT_SOFTMAX));
-        if (!ok) break;
-        ++n_o;
-        tc_fence_after();
-      }
-      const float inv_l = (it > 0 && l > 0.f) ? (1.0f / l) : 0.f;
-      __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
-      const __nv_bfloat16* irow =
-          (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
-      // accumulate input taken from a coarser token grid: this row's four source tokens and weights
-      const bool resize = (MODE == MODE_CSP) && p.oi_side > 0;
-      BilinearTaps tp = {};
-      const __nv_bfloat16* ibase = nullptr;
-      if (resize && row_ok) {
-        tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
-        ibase = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
-      }
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
+      if (MODE != MODE_CS_ONLY) {
         if (it > 0) {
-          tmem_ld_x32(tO + c * 32, r);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, wc, DEV_TIMEOUT_SOFTMAX));
+          if (!ok) break;
+          ++n_o;
+          tc_fence_after();
         }
-        if (c == D / 32 - 1 && it > 0) {
-          // O has been read out of TMEM: the MMA warp may overwrite it for the next item
-          tc_fence_before();
-          mbar_arrive(&bars->o_empty[s]);
+        const float inv_l = (it > 0 && l > 0.f) ? (1.0f / l) : 0.f;
+        __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
+        const __nv_bfloat16* irow =
+            (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
+        // accumulate input taken from a coarser token grid: this row's four source tokens and weights
+        const bool resize = (MODE == MODE_CSP) && p.oi_side > 0;
+        BilinearTaps tp = {};
+        const __nv_bfloat16* ibase = nullptr;
+        if (resize && row_ok) {
+          tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
+          ibase = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
         }
-        if (row_ok) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint32_t w[4];
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          if (it > 0) {
+            tmem_ld_x32(tO + c * 32, r);
+            tmem_wait_ld();
+          } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float x0 = __uint_as_float(r[q4 * 8 + 2 * i]) * inv_l;
-              const float x1 = __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l;
-              w[i] = pack_bf16x2(x0, x1);
-            }
-            if (MODE == MODE_CSP) {
-              // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
-              // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
-              uint4 prev;
-              if (resize) {
-                const __nv_bfloat16* ib = ibase + c * 32 + q4 * 8;
-                prev = bilinear_mix8(tp, *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r00 * p.oi_sl),
-                                     *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r01 * p.oi_sl),
-                                     *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r10 * p.oi_sl),
-                                     *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r11 * p.oi_sl));
-              } else {
-                prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
-              }
-              const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (c == D / 32 - 1 && it > 0) {
+            // O has been read out of TMEM: the MMA warp may overwrite it for the next item
+            tc_fence_before();
+            mbar_arrive(&bars->o_empty[s]);
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint32_t w[4];
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                const float d0 = __uint_as_float(w[i] << 16), d1 = __uint_as_float(w[i] & 0xffff0000u);
-                const float a0 = __uint_as_float(pv[i] << 16), a1 = __uint_as_float(pv[i] & 0xffff0000u);
-                w[i] = pack_bf16x2(fmaf(p.o_scale, d0, a0), fmaf(p.o_scale, d1, a1));
+                const float x0 = __uint_as_float(r[q4 * 8 + 2 * i]) * inv_l;
+                const float x1 = __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l;
+                w[i] = pack_bf16x2(x0, x1);
               }
+              if (MODE == MODE_CSP) {
+                // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
+                // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
+                uint4 prev;
+                if (resize) {
+                  const __nv_bfloat16* ib = ibase + c * 32 + q4 * 8;
+                  prev = bilinear_mix8(tp, *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r00 * p.oi_sl),
+                                       *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r01 * p.oi_sl),
+                                       *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r10 * p.oi_sl),
+                                       *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r11 * p.oi_sl));
+                } else {
+                  prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
+                }
+                const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float d0 = __uint_as_float(w[i] << 16), d1 = __uint_as_float(w[i] & 0xffff0000u);
+                  const float a0 = __uint_as_float(pv[i] << 16), a1 = __uint_as_float(pv[i] & 0xffff0000u);
+                  w[i] = pack_bf16x2(fmaf(p.o_scale, d0, a0), fmaf(p.o_scale, d1, a1));
+                }
+              }
+              *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
-      if (row_ok && MODE != MODE_CSP) {
+      if (stats_given) {
+        // M = row maximum, L = row sum relative to it (both in log2 units of the scaled scores)
+        const int64_t si = (int64_t)im.bh * p.Lq + row;
+        m_ref = row_ok ? p.M_in[si] : -INFINITY;
+        l = row_ok ? p.L_in[si] : 0.f;
+      } else if (row_ok && MODE != MODE_CSP) {
         const int64_t si = (int64_t)im.bh * p.Lq + row;
         if (p.M) p.M[si] = m_true;
         if (p.L) p.L[si] = (it > 0 && l > 0.f) ? l * fast_exp2(m_ref - m_true) : 0.f;
       }
-      if (MODE == MODE_DENSE_CS && n_mine > 0) {
+      if (kHasCs && n_mine > 0) {
         // ---- second sweep: column sums of this slot's query tile.  S^T = K Q^T lands in S_s with one KEY per
         // TMEM lane, so this thread owns key column j*128 + r_in_tile and sums the 128 probabilities
         // p_i = exp2(s_i * scale - (M_i + log2 L_i)) of the tile's queries in registers.
         negc[s * 128 + r_in_tile] = (row_ok && l > 0.f) ? -(m_ref + log2f(l)) : -INFINITY;
         wg_sync(s);  // the warpgroup's 128 constants are in place
         const float4* nc4 = reinterpret_cast<const float4*>(negc + s * 128);
+        // a tile with fewer than 128 queries carries -inf constants, which the polynomial cannot take
+        const bool full_tile = im.row_end[s] - im.row0[s] >= 128;
         const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
         const int tile = im.row0[s] >> 7;
         float* cs_row = p.cs + im.b * p.cs_sb + im.h * p.cs_sh + (int64_t)tile * p.cs_st;
-        for (int j = 0; j < n_mine; ++j) {
-          // tile j of the sweep sits in buffer j % kCsBufs: S_s, or the (by now written out) O region
-          const int buf = j % kCsBufs;
-          ok = __all_sync(0xffffffffu, mbar_wait(&bars->cs_full[s][buf], n_cs[buf] & 1, wc, DEV_TIMEOUT_SOFTMAX));
-          if (!ok) break;
-          ++n_cs[buf];
-          tc_fence_after();
-          const uint32_t tT = buf == 0 ? tS : tmem_base + lane_off + TM_O + (uint32_t)s * 128u;
-          float acc = 0.f;
+        // the sweep over the KV tiles, compiled twice: the exponential mix is a compile-time choice (a run-time
+        // choice per chunk measured 20 % slower)
+        auto cs_sweep = [&](auto poly_tag) -> bool {
+          constexpr uint32_t POLY = decltype(poly_tag)::value;
+          for (int j = 0; j < n_mine; ++j) {
+            // tile j of the sweep sits in buffer j % kCsBufs: S_s, or the (by now written out) O region
+            const int buf = j % kCsBufs;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->cs_full[s][buf], n_cs[buf] & 1, wc, DEV_TIMEOUT_SOFTMAX));
+            if (!ok) return false;
+            ++n_cs[buf];
+            tc_fence_after();
+            const uint32_t tT = buf == 0 ? tS : tmem_base + lane_off + TM_O + (uint32_t)s * 128u;
+            float acc = 0.f;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_x32(tT + c * 32, r);
-            tmem_wait_ld();
-            uint64_t a = 0ull, bsum = 0ull;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 nc = nc4[c * 8 + i];
-              const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])), sc2,
-                                        pack_f32x2(nc.x, nc.y));
-              const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), sc2,
-                                        pack_f32x2(nc.z, nc.w));
-              float x0, x1, y0, y1;
-              unpack_f32x2(t0, x0, x1);
-              unpack_f32x2(t1, y0, y1);
-              a = fadd2(a, pack_f32x2(fast_exp2(x0), fast_exp2(x1)));
-              bsum = fadd2(bsum, pack_f32x2(fast_exp2(y0), fast_exp2(y1)));
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tmem_ld_x32(tT + c * 32, r);
+              tmem_wait_ld();
+              acc += colsum_chunk<POLY>(r, nc4 + c * 8, sc2);
             }
-            float a0, a1, b0, b1;
-            unpack_f32x2(a, a0, a1);
-            unpack_f32x2(bsum, b0, b1);
-            acc += (a0 + a1) + (b0 + b1);
+            // S^T has been read: the MMA warp may overwrite the buffer with the tile after the next
+            tc_fence_before();
+            mbar_arrive(&bars->cs_empty[s][buf]);
+            const int key = j * 128 + r_in_tile;
+            if (key < p.Lkv) cs_row[key] = acc;
           }
-          // S^T has been read: the MMA warp may overwrite the buffer with the tile after the next
-          tc_fence_before();
-          mbar_arrive(&bars->cs_empty[s][buf]);
-          const int key = j * 128 + r_in_tile;
-          if (key < p.Lkv) cs_row[key] = acc;
-        }
+          return true;
+        };
+        ok = full_tile ? cs_sweep(std::integral_constant<uint32_t, kCsPolyMask>{})
+                       : cs_sweep(std::integral_constant<uint32_t, 0u>{});
         if (!ok) break;
         wg_sync(s);  // nobody still reads the constants
       }
@@ -555,7 +584,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         if (MODE != MODE_CSP) {
           // MODE_DENSE_CS streams the K tiles a second time for the column-sum sweep
-          const int sweeps = MODE == MODE_DENSE_CS ? 2 : 1;
+          const int sweeps = (kHasCs && !stats_given) ? 2 : 1;
           for (int rr = 0; rr < sweeps * rounds && ok; ++rr) {
             const int r = rr < rounds ? rr : rr - rounds;
             const Round rd = round_info(l0, l1, e, r);
@@ -635,7 +664,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
         const uint16_t* l1 = l0 + kMaxSteps;
         const int rounds = max(e.n0, e.n1);
-        if (MODE != MODE_CSP) {
+        if (MODE == MODE_CS_ONLY) {
+          // no V in this mode: the warp only follows the schedule
+        } else if (MODE != MODE_CSP) {
           for (int r = 0; r < rounds && ok; ++r) {
             const Round rd = round_info(l0, l1, e, r);
             for (int s = 0; s < 2; ++s) {
@@ -726,11 +757,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         prev.kvb[0] = prev.kvb[1] = 0;
         int pvs[2] = {0, 0}, pvp[2] = {0, 0};  // V stage / parity of the previous round, per slot
         int npv[2] = {0, 0};
-        for (int r = 0; r <= rounds && ok; ++r) {
+        const int rounds_first = stats_given ? 0 : rounds;
+        for (int r = 0; r <= rounds_first && ok; ++r) {
           Round cur;
           cur.has[0] = cur.has[1] = cur.shared = false;
           cur.kvb[0] = cur.kvb[1] = 0;
-          if (r < rounds) cur = round_info(l0, l1, e, r);
+          if (r < rounds_first) cur = round_info(l0, l1, e, r);
           // stages of this round's tiles (same order as the loaders issue them)
           int ks[2] = {0, 0}, kp[2] = {0, 0}, vs[2] = {0, 0}, vp[2] = {0, 0};
           for (int s = 0; s < 2; ++s) {
@@ -743,7 +775,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             vs[s] = vc % kStages; vp[s] = (vc / kStages) & 1; ++vc;
           }
           for (int s = 0; s < 2 && ok; ++s) {
-            if (prev.has[s]) {
+            if (prev.has[s] && MODE == MODE_CS_ONLY) {
+              // statistics sweep: no PV; S_s is free again once the softmax warps have read the last product
+              ok = mbar_wait(&bars->p_full[s], n_p[s] & 1, wc, DEV_TIMEOUT_MMA);
+              if (!ok) break;
+              ++n_p[s];
+            } else if (prev.has[s]) {
               if (!(s == 1 && prev.shared)) {
                 ok = mbar_wait(&bars->v_full[pvs[s]], pvp[s], wc, DEV_TIMEOUT_MMA);
                 if (!ok) break;
@@ -799,7 +836,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ++n_o[s];
           }
         }
-        if (MODE == MODE_DENSE_CS) {
+        if (kHasCs) {
           // ---- column-sum sweep: S_s^T = K Q_s^T per KV tile (the operands swap roles, the tiles stay where
           // they are); a slot's next product waits until its softmax warps have read the previous one.
           for (int r = 0; r < rounds && ok; ++r) {
@@ -998,25 +1035,34 @@ int launch_d(int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     case MODE_DENSE: return launch_mode<D, MODE_DENSE>(tq, tk, tv, p, grid, stream);
     case MODE_BLOCK: return launch_mode<D, MODE_BLOCK>(tq, tk, tv, p, grid, stream);
     case MODE_DENSE_CS: return launch_mode<D, MODE_DENSE_CS>(tq, tk, tv, p, grid, stream);
+    case MODE_CS_ONLY: return launch_mode<D, MODE_CS_ONLY>(tq, tk, tv, p, grid, stream);
     default: return launch_mode<D, MODE_CSP>(tq, tk, tv, p, grid, stream);
   }
 }
 
 }  // namespace
 
+// mode: an AttnMode, or MODE_CS_ONLY + 1 for the column sums from row statistics the caller supplies in
+// a->M / a->L.
 int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   LVAR_REQUIRE(a != nullptr, LVAR_ERR_ARG, "null argument block");
+  const bool stats_given = mode == MODE_CS_ONLY + 1;
+  if (stats_given) mode = MODE_CS_ONLY;
   LVAR_REQUIRE(a->D == 64 || a->D == 128, LVAR_ERR_UNSUPPORTED, "Head dimension must be 64 or 128 (got %d)", a->D);
   LVAR_REQUIRE(a->B >= 1 && a->H >= 1 && a->Lq >= 1 && a->Lkv >= 1, LVAR_ERR_ARG,
                "B, H, Lq, Lkv must be >= 1 (got %d %d %d %d)", a->B, a->H, a->Lq, a->Lkv);
-  LVAR_REQUIRE(a->q && a->k && a->v && a->o, LVAR_ERR_ARG, "q, k, v, o must be non-null device pointers");
-  LVAR_REQUIRE(aligned16(a->q) && aligned16(a->k) && aligned16(a->v) && aligned16(a->o), LVAR_ERR_ARG,
+  // the column sums alone read neither v nor o
+  const bool qk_only = mode == MODE_CS_ONLY;
+  LVAR_REQUIRE(a->q && a->k && (qk_only || (a->v && a->o)), LVAR_ERR_ARG,
+               "q, k, v, o must be non-null device pointers");
+  LVAR_REQUIRE(aligned16(a->q) && aligned16(a->k) && (qk_only || (aligned16(a->v) && aligned16(a->o))), LVAR_ERR_ARG,
                "q, k, v, o must be 16-byte aligned");
   LVAR_REQUIRE(a->scale > 0.f && isfinite(a->scale), LVAR_ERR_ARG, "softmax scale must be positive and finite");
   const int64_t strides[] = {a->q_sb, a->q_sh, a->q_sl, a->k_sb, a->k_sh, a->k_sl,
                              a->v_sb, a->v_sh, a->v_sl, a->o_sb, a->o_sh, a->o_sl};
-  for (int64_t s : strides)
-    LVAR_REQUIRE(s % 8 == 0 && s >= 0, LVAR_ERR_ARG, "tensor strides must be non-negative multiples of 8 elements");
+  for (int i = 0; i < (qk_only ? 6 : 12); ++i)
+    LVAR_REQUIRE(strides[i] % 8 == 0 && strides[i] >= 0, LVAR_ERR_ARG,
+                 "tensor strides must be non-negative multiples of 8 elements");
 
   AttnParams p{};
   p.B = a->B;
@@ -1031,7 +1077,13 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   p.o_sl = a->o_sl;
   p.M = a->M;
   p.L = a->L;
-  if (mode == MODE_DENSE_CS) {
+  if (stats_given) {
+    LVAR_REQUIRE(a->M && a->L, LVAR_ERR_ARG, "M and L (row statistics, fp32 [B,H,Lq]) must be non-null");
+    p.M_in = a->M;
+    p.L_in = a->L;
+    p.M = p.L = nullptr;
+  }
+  if (mode == MODE_DENSE_CS || mode == MODE_CS_ONLY) {
     LVAR_REQUIRE(a->cs != nullptr, LVAR_ERR_ARG, "cs (column sums per 128-row query tile) is null");
     p.cs = a->cs;
     p.cs_sb = a->cs_sb;
@@ -1060,7 +1112,7 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     p.m_sh = a->bm_sh;
     p.m_sq = a->bm_sq;
   }
-  if (mode == MODE_DENSE) {
+  if (mode == MODE_DENSE || mode == MODE_DENSE_CS || mode == MODE_CS_ONLY) {
     LVAR_REQUIRE(p.nkb <= 16383, LVAR_ERR_UNSUPPORTED, "Lkv too long (max %d keys)", 16383 * 128);
   }
   if (mode == MODE_CSP) {
@@ -1129,8 +1181,12 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   if (rc != LVAR_OK) return rc;
   rc = encode_bhld_map(&tk, a->k, a->B, a->H, a->Lkv, a->D, a->k_sb, a->k_sh, a->k_sl, 128);
   if (rc != LVAR_OK) return rc;
-  rc = encode_bhld_map(&tv, a->v, a->B, a->H, a->Lkv, a->D, a->v_sb, a->v_sh, a->v_sl, 128);
-  if (rc != LVAR_OK) return rc;
+  if (qk_only) {
+    tv = tk;  // never used by the kernel in this mode
+  } else {
+    rc = encode_bhld_map(&tv, a->v, a->B, a->H, a->Lkv, a->D, a->v_sb, a->v_sh, a->v_sl, 128);
+    if (rc != LVAR_OK) return rc;
+  }
 
   if (a->D == 128) return launch_d<128>(mode, tq, tk, tv, p, grid, stream);
   return launch_d<64>(mode, tq, tk, tv, p, grid, stream);

@@ -118,6 +118,66 @@ def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=Non
     return (o, cs, M, L) if return_stats else (o, cs)
 
 
+def colsum_tiles_fwd(q, k, scale=None, *, stats=None, return_stats=False, status=None):
+    """Attention column sums of every 128-row query tile without the attention output: fp32
+    [B,H,ceil(Lq/128),Lkv].  ``stats`` = (M, L) as ``dense_attn_fwd`` returns them skips the statistics sweep;
+    otherwise one launch takes them first (``return_stats`` hands them back)."""
+    _require_cuda_bf16("q", q)
+    _require_cuda_bf16("k", k)
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    if k.shape[0] != B or k.shape[1] != H or k.shape[3] != D:
+        raise RuntimeError(f"q/k shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}")
+    cs = torch.empty((B, H, (Lq + 127) // 128, Lkv), dtype=torch.float32, device=q.device)
+    a = AttnArgs()
+    a.B, a.H, a.Lq, a.Lkv, a.D = B, H, Lq, Lkv, D
+    a.scale = float(D ** -0.5 if scale is None else scale)
+    a.q, a.q_sb, a.q_sh, a.q_sl = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
+    a.k, a.k_sb, a.k_sh, a.k_sl = k.data_ptr(), k.stride(0), k.stride(1), k.stride(2)
+    a.wait_limit_ns = _lib.DEFAULT_WAIT_NS
+    a.sched_scratch = _sched_scratch(q.device).data_ptr()
+    a.cs, a.cs_sb, a.cs_sh, a.cs_st = cs.data_ptr(), cs.stride(0), cs.stride(1), cs.stride(2)
+    M = L = None
+    if stats is not None:
+        M, L = stats
+        for n, t in (("M", M), ("L", L)):
+            if t.dtype != torch.float32 or not t.is_cuda or t.numel() != B * H * Lq or not t.is_contiguous():
+                raise RuntimeError(f"{n} must be a contiguous CUDA float32 tensor with B*H*Lq elements")
+        a.M, a.L = M.data_ptr(), L.data_ptr()
+    elif return_stats:
+        M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        L = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        a.M, a.L = M.data_ptr(), L.data_ptr()
+    if status is not None:
+        a.dev_status = status.data_ptr()
+    check(lib.lvar_colsum_tiles(C.byref(a), 1 if stats is not None else 0, _stream_ptr(q.device)))
+    return (cs, M, L) if return_stats else cs
+
+
+def sum_tiles(cs128: torch.Tensor, per: int) -> torch.Tensor:
+    """Column sums of groups of ``per`` adjacent 128-row query tiles: [B,H,T,Lkv] -> [B,H,ceil(T/per),Lkv],
+    added in a fixed order (bit-reproducible)."""
+    if per == 1:
+        return cs128
+    B, H, T, Lkv = cs128.shape
+    G = (T + per - 1) // per
+    if T != G * per:
+        cs128 = torch.nn.functional.pad(cs128, (0, 0, 0, G * per - T))
+    parts = cs128.view(B, H, G, per, Lkv)
+    cs = parts[:, :, :, 0]
+    for i in range(1, per):
+        cs = cs + parts[:, :, :, i]
+    return cs
+
+
+def colsum_groups_fwd(q, k, M, L, group_rows, scale=None):
+    """Column sums per group of ``group_rows`` query rows from given row statistics: the transposed sweep of
+    the attention kernel when the group is a multiple of 128 rows, the stand-alone kernel otherwise."""
+    if group_rows % 128 == 0:
+        return sum_tiles(colsum_tiles_fwd(q, k, scale, stats=(M, L)), group_rows // 128)
+    return colsum_fwd(q, k, M, L, group_rows, scale)
+
+
 def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None, block=128):
     """Attention under a block mask of 128x128 (or 64x64) blocks: uint8/bool [nq,nk], [H,nq,nk] or [B,H,nq,nk]."""
     for n, t in (("q", q), ("k", k), ("v", v)):

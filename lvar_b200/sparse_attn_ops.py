@@ -39,17 +39,7 @@ def _dense_colsum(q, k, v, scale):
         # one launch: the attention kernel sweeps the K tiles a second time for the column sums of its 128-row
         # query tiles; a group of pad_to rows is pad_to / 128 adjacent tiles, added in a fixed order
         o, cs128 = K.dense_colsum_attn_fwd(q, k, v, scale)
-        per = pad_to // 128
-        if per == 1:
-            cs = cs128
-        else:
-            B, H, T, Lkv = cs128.shape
-            G = (T + per - 1) // per
-            if T != G * per:
-                cs128 = torch.nn.functional.pad(cs128, (0, 0, 0, G * per - T))
-            cs = cs128.view(B, H, G, per, Lkv)[:, :, :, 0]
-            for i in range(1, per):
-                cs = cs + cs128.view(B, H, G, per, Lkv)[:, :, :, i]
+        cs = K.sum_tiles(cs128, pad_to // 128)
     else:
         o, M, L = K.dense_attn_fwd(q, k, v, scale)
         cs = K.colsum_fwd(q, k, M, L, pad_to, scale)

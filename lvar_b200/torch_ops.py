@@ -47,7 +47,7 @@ def _dense_colsum_attn_scaled(q, k, v, p, scale: float):
     B, H, Lq, _ = q.shape
     # p = 1/sum exp(s): in the kernel's base-2 form that is M' = -log2(p), L' = 1
     Mp = (-torch.log2(p.reshape(B, H, Lq).float())).contiguous()
-    cs = K.colsum_fwd(q, k, Mp, torch.ones_like(Mp), get_kernel_config_attn()["bm"], scale)
+    cs = K.colsum_groups_fwd(q, k, Mp, torch.ones_like(Mp), get_kernel_config_attn()["bm"], scale)
     return [o, cs, _l_vec(M, L)]
 
 

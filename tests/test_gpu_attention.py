@@ -264,6 +264,30 @@ def test_fused_dense_colsum_matches_separate_kernels_and_oracle(K, B, H, Lq, Lkv
     assert torch.equal(o2, o) and torch.equal(cs2, cs)
 
 
+@pytest.mark.parametrize("B,H,Lq,Lkv,D", [(1, 2, 700, 900, 64), (2, 3, 1000, 1300, 128), (1, 1, 100, 77, 128),
+                                          (1, 2, 1, 300, 128), (2, 80, 512, 640, 64)])
+def test_colsum_tiles_without_output_matches_fused_launch(K, B, H, Lq, Lkv, D):
+    """Column sums alone (statistics sweep without P and PV, then the transposed sweep): the sums and the row
+    statistics are the fused attention + column-sum launch's bit for bit; with the statistics supplied by the
+    caller only the second sweep runs and agrees to rounding.  More work items than SMs in the last case."""
+    from oracle import attention as oa
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq + 1)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    _, want, M0, L0 = K.dense_colsum_attn_fwd(qc, kc, vc, return_stats=True)
+    st = K.new_status("cuda")
+    cs, M, L = K.colsum_tiles_fwd(qc, kc, return_stats=True, status=st)
+    _ok_status(K, st)
+    assert torch.equal(cs, want) and torch.equal(M, M0) and torch.equal(L, L0)
+    st = K.new_status("cuda")
+    cs2 = K.colsum_tiles_fwd(qc, kc, stats=(M0, L0), status=st)
+    _ok_status(K, st)
+    assert ((cs2 - want).abs() <= 1e-5 * want.abs().max()).all()
+    assert torch.equal(K.colsum_tiles_fwd(qc, kc), cs)  # back to back on one stream
+    if B * H <= 6:
+        _, ref = oa.dense_colsum_attn(q, k, v, None, q_group_size=128, dtype=torch.float64)
+        assert ((cs.cpu().double() - ref.double()).abs().max() / ref.double().abs().max()).item() <= CS_REL
+
+
 @pytest.mark.parametrize("s_side,t_side,D,bm", [(12, 16, 128, 256), (5, 13, 64, 64), (16, 16, 128, 192), (20, 17, 64, 256)])
 def test_csp_attn_with_resized_ocache_matches_two_launches(K, s_side, t_side, D, bm):
     """The O-cache resize inside the attention epilogue gives the bits of the stand-alone resize kernel followed

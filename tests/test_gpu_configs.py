@@ -45,10 +45,13 @@ def test_per_scale_colsum_and_token_topk(K):
         Lq, Lkv = s * s, cum[si + 1]
         q = q_all[:, :, cum[si]:cum[si + 1]].contiguous()
         k, v = k_all[:, :, :Lkv], v_all[:, :, :Lkv]
-        group = (Lq + 31) // 32 * 32
-        o, M, L = K.dense_attn_fwd(q, k, v, scale)
-        cs = K.colsum_fwd(q, k, M, L, group, scale)
+        # scores only: no attention output is formed; the per-tile sums are added in a fixed order
+        cs = K.colsum_tiles_fwd(q, k, scale).sum(dim=2, keepdim=True)
         assert cs.shape == (B, H, 1, Lkv)
+        if si in (3, 9):  # the stand-alone kernel fed with the dense kernel's row statistics agrees
+            _, M, L = K.dense_attn_fwd(q, k, v, scale)
+            sep = K.colsum_fwd(q, k, M, L, (Lq + 31) // 32 * 32, scale)
+            assert ((cs - sep).abs() <= 1e-4 * sep.abs().max()).all()
         assert torch.allclose(cs.sum(-1), torch.full((B, H, 1), float(Lq), device="cuda"), rtol=1e-3)
         if Lkv <= 2521:  # direct check against PyTorch on the GPU for the small scales
             p = torch.softmax((q.float() @ k.float().transpose(-1, -2)) * scale, dim=-1).sum(2, keepdim=True)
