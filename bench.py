@@ -279,6 +279,21 @@ def run_ours(args):
         cs4a_us[f"scale{si}_{'decision' if full else 'sparse'}_q{lq}_k{lk}"] = 1e3 * timed(one_call, 10, warm=3)
     del layer, qs
 
+    # ---- per-scale KV scoring of the 13-scale schedule: the column sums of each scale's queries over all keys
+    # so far, one score row per head (no attention output), then the ascending top-k that keeps 10 % of them
+    kv_score_us = {}
+    for si, s_ in enumerate(P.INFINITY_SCALES):
+        lk = cum[si + 1]
+        keep = round(0.1 * lk)
+        qs, ks = torch.randn(B, H, s_ * s_, D, device=dev, generator=gq).bfloat16(), k[:, :, :lk]
+
+        def score():
+            cs_row = K.colsum_tiles_fwd(qs, ks, scale).sum(dim=2, keepdim=True)
+            return K.topk_indices(cs_row, keep, ascending_index=True) if keep else cs_row
+        kv_score_us[f"scale{si}_q{s_ * s_}_k{lk}_keep{keep}"] = round(1e3 * timed(score, 10, warm=3), 1)
+    kv_score_us["total"] = round(sum(kv_score_us.values()), 1)
+    del qs, ks
+
     # ---- timed region: K steps of block-sparse attention, inputs resident in HBM
     step = lambda: K.block_sparse_attn_fwd(q, k, v, mask, scale)  # noqa: E731
     # at least 20 untimed steps: the SM clock of this power-limited part settles over the first launches of a
@@ -392,7 +407,7 @@ def run_ours(args):
                   "mask_build_us": mask_ms * 1e3, "density": K_TOTAL / nk,
                   "csp_attn_us": csp_ms * 1e3, "csp_attn_tflops": csp_flops / csp_ms / 1e9,
                   "csp_attn_workload": f"{csp_top} scattered + {csp_band} consecutive keys per {csp_bm}-row group",
-                  "cs4a_layer_us": cs4a_us},
+                  "cs4a_layer_us": cs4a_us, "kv_scoring_colsum_topk_us": kv_score_us},
     }
     if world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
