@@ -288,6 +288,28 @@ def test_colsum_tiles_without_output_matches_fused_launch(K, B, H, Lq, Lkv, D):
         assert ((cs.cpu().double() - ref.double()).abs().max() / ref.double().abs().max()).item() <= CS_REL
 
 
+def test_colsum_groups_from_given_stats_and_argument_checks(K):
+    """Groups that are multiples of 128 rows take the transposed sweep of the attention kernel and agree with
+    the stand-alone kernel (which serves every multiple of 32); bad arguments are refused before any launch."""
+    q, k, v = _qkv(2, 2, 900, 1100, 128, seed=21)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    _, M, L = K.dense_attn_fwd(qc, kc, vc)
+    for group in (128, 256, 384):
+        got = K.colsum_groups_fwd(qc, kc, M, L, group)
+        want = K.colsum_fwd(qc, kc, M, L, group)
+        assert got.shape == want.shape == (2, 2, (900 + group - 1) // group, 1100)
+        assert ((got - want).abs() <= 1e-5 * want.abs().max()).all()
+    assert torch.equal(K.colsum_groups_fwd(qc, kc, M, L, 96), K.colsum_fwd(qc, kc, M, L, 96))
+    t = torch.arange(2 * 3 * 5 * 7, dtype=torch.float32, device="cuda").view(2, 3, 5, 7)
+    assert torch.equal(K.sum_tiles(t, 2)[:, :, 2], t[:, :, 4]) and torch.equal(K.sum_tiles(t, 2)[:, :, 0], t[:, :, 0] + t[:, :, 1])
+    with pytest.raises(RuntimeError):
+        K.colsum_tiles_fwd(qc, kc[:, :1])                       # head mismatch
+    with pytest.raises(RuntimeError):
+        K.colsum_tiles_fwd(qc, kc, stats=(M[:, :, :-1].contiguous(), L))  # statistics of another shape
+    with pytest.raises(RuntimeError):
+        K.colsum_tiles_fwd(qc.float(), kc)                      # not bf16
+
+
 @pytest.mark.parametrize("s_side,t_side,D,bm", [(12, 16, 128, 256), (5, 13, 64, 64), (16, 16, 128, 192), (20, 17, 64, 256)])
 def test_csp_attn_with_resized_ocache_matches_two_launches(K, s_side, t_side, D, bm):
     """The O-cache resize inside the attention epilogue gives the bits of the stand-alone resize kernel followed
