@@ -279,6 +279,29 @@ def run_ours(args):
         cs4a_us[f"scale{si}_{'decision' if full else 'sparse'}_q{lq}_k{lk}"] = 1e3 * timed(one_call, 10, warm=3)
     del layer, qs
 
+    # ---- the same three steps of one layer captured in one CUDA graph (they make no host synchronisation and
+    # allocate only from the graph's pool) and replayed: what is left of the per-launch host cost
+    layer = P.SparseDiffAttn(layer_num=0)
+    steps_in = [(si, full, torch.randn(B, H, P.INFINITY_SCALES[si] ** 2, D, device=dev, generator=gq).bfloat16())
+                for si, full in ((10, True), (11, False), (12, False))]
+
+    def three_steps():
+        return [layer(qs_, k[:, :, :cum[si + 1]], v[:, :, :cum[si + 1]], scale, do_full_step=full, scale_ind=si)
+                for si, full, qs_ in steps_in]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            three_steps()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    layer_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(layer_graph, stream=side):
+        graph_out = three_steps()
+    cs4a_us["three_steps_eager_sum"] = sum(cs4a_us.values())
+    cs4a_us["three_steps_one_graph_replay"] = 1e3 * timed(layer_graph.replay, 10, warm=3)
+    del layer, layer_graph, graph_out, steps_in
+
     # ---- per-scale KV scoring of the 13-scale schedule: the column sums of each scale's queries over all keys
     # so far, one score row per head (no attention output), then the ascending top-k that keeps 10 % of them
     kv_score_us = {}
@@ -292,7 +315,28 @@ def run_ours(args):
             return K.topk_indices(cs_row, keep, ascending_index=True) if keep else cs_row
         kv_score_us[f"scale{si}_q{s_ * s_}_k{lk}_keep{keep}"] = round(1e3 * timed(score, 10, warm=3), 1)
     kv_score_us["total"] = round(sum(kv_score_us.values()), 1)
-    del qs, ks
+    # all 13 scales in one CUDA graph: the small scales are launch-bound when issued from Python
+    q_sc = [torch.randn(B, H, s_ * s_, D, device=dev, generator=gq).bfloat16() for s_ in P.INFINITY_SCALES]
+
+    def score_all():
+        out = []
+        for si in range(len(P.INFINITY_SCALES)):
+            lk = cum[si + 1]
+            cs_row = K.colsum_tiles_fwd(q_sc[si], k[:, :, :lk], scale).sum(dim=2, keepdim=True)
+            keep = round(0.1 * lk)
+            out.append(K.topk_indices(cs_row, keep, ascending_index=True) if keep else cs_row)
+        return out
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            score_all()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    score_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(score_graph, stream=side):
+        score_out = score_all()
+    kv_score_us["total_one_graph_replay"] = round(1e3 * timed(score_graph.replay, 10, warm=3), 1)
+    del qs, ks, q_sc, score_graph, score_out
 
     # ---- timed region: K steps of block-sparse attention, inputs resident in HBM
     step = lambda: K.block_sparse_attn_fwd(q, k, v, mask, scale)  # noqa: E731

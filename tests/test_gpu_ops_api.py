@@ -176,6 +176,57 @@ def test_sparse_diff_attn_full_then_sparse_steps(ops):
         GLOBAL_CONFIG["attn"]["top_keys"] = saved
 
 
+def test_cs4a_layer_replays_as_a_cuda_graph(ops):
+    """A layer's decision step and its two sparse steps captured in one CUDA graph: no host synchronisation,
+    no allocation outside the graph's pool, the persistent kernels' work counters reset themselves.  Replays
+    give the eager results bit for bit, also after the static inputs have been overwritten."""
+    from lvar_b200 import policy as P
+    scales = [2, 4, 16, 24, 32]
+    cum = P.cumulative_tokens(scales)
+    B, H, D = 1, 2, 64
+    scale = 1.0 / math.sqrt(D)
+
+    def inputs(seed):
+        g = torch.Generator().manual_seed(seed)
+        kv = torch.randn(B, H, cum[-1], D, generator=g).bfloat16().cuda()
+        vv = torch.randn(B, H, cum[-1], D, generator=g).bfloat16().cuda()
+        qs = [torch.randn(B, H, scales[s] ** 2, D, generator=g).bfloat16().cuda() for s in (2, 3, 4)]
+        return kv, vv, qs
+
+    def layer_steps(attn, kv, vv, qs):
+        outs = []
+        for i, s in enumerate((2, 3, 4)):
+            outs.append(attn(qs[i], kv[:, :, :cum[s + 1]], vv[:, :, :cum[s + 1]], scale, do_full_step=(s == 2),
+                             scale_ind=s))
+        return outs
+
+    eager = {seed: [o.clone() for o in layer_steps(P.SparseDiffAttn(layer_num=0, scales=scales, spsd_scale=2,
+                                                                   wind_size=[3, 5]), *inputs(seed))]
+             for seed in (1, 2)}
+    attn = P.SparseDiffAttn(layer_num=0, scales=scales, spsd_scale=2, wind_size=[3, 5])
+    kv, vv, qs = inputs(1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # warm-up on the capture stream: caches, scratch and kernel attributes are set here
+            layer_steps(attn, kv, vv, qs)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        outs = layer_steps(attn, kv, vv, qs)
+    for seed in (1, 2, 1):
+        kv2, vv2, qs2 = inputs(seed)
+        kv.copy_(kv2)
+        vv.copy_(vv2)
+        for a, b in zip(qs, qs2):
+            a.copy_(b)
+        graph.replay()
+        torch.cuda.synchronize()
+        for got, want in zip(outs, eager[seed]):
+            assert torch.equal(got, want)
+
+
 def test_sparse_flex_attn_class(ops):
     from lvar_b200 import policy as P
     from oracle import attention as oa
