@@ -923,6 +923,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       int n0 = 0, n1 = 0, aux = 0;
       if (item >= 0) {
         const Item im = decode(item);
+        // The item's Q tiles are read once in the whole launch, so they come from HBM, and their load sits
+        // between two items with nothing to overlap it: start them towards L2 now, one item ahead.
+        if (lane < 2 * NSUB && ((im.live >> (lane / NSUB)) & 1u))
+          tma_prefetch_l2_4d(&tmQ, (lane % NSUB) * 64, lane < NSUB ? im.row0[0] : im.row0[1], im.h, im.b);
         uint16_t* l0 = lists + (slot * 2) * kMaxSteps;
         uint16_t* l1 = l0 + kMaxSteps;
         if (MODE == MODE_BLOCK) {
