@@ -15,8 +15,11 @@ from . import _lib
 from ._lib import AttnArgs, check, lib
 
 
+_raw_stream = torch._C._cuda_getCurrentRawStream  # (device index) -> cudaStream_t of torch's current stream
+
+
 def _stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
 
 
 def _require_cuda_bf16(name: str, t: torch.Tensor) -> None:
@@ -30,7 +33,8 @@ def _require_cuda_bf16(name: str, t: torch.Tensor) -> None:
         raise RuntimeError(f"{name} must have a contiguous last dimension")
 
 
-def _fill_qkv(a: AttnArgs, q, k, v, o, scale) -> None:
+def _fill_qkv(a: AttnArgs, q, k, v, o, scale) -> int:
+    """Fills the problem, tensor and scheduling fields; returns the stream to launch on."""
     B, H, Lq, D = q.shape
     if k.shape[0] != B or k.shape[1] != H or v.shape[:2] != k.shape[:2]:
         raise RuntimeError(f"q/k/v batch or head mismatch (query heads must equal kv heads): "
@@ -39,28 +43,28 @@ def _fill_qkv(a: AttnArgs, q, k, v, o, scale) -> None:
         raise RuntimeError(f"q/k/v shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
     a.B, a.H, a.Lq, a.Lkv, a.D = B, H, Lq, k.shape[2], D
     a.scale = float(D ** -0.5 if scale is None else scale)
-    for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
-        setattr(a, name, t.data_ptr())
-        setattr(a, name + "_sb", t.stride(0))
-        setattr(a, name + "_sh", t.stride(1))
-        setattr(a, name + "_sl", t.stride(2))
+    a.q, (a.q_sb, a.q_sh, a.q_sl, _) = q.data_ptr(), q.stride()
+    a.k, (a.k_sb, a.k_sh, a.k_sl, _) = k.data_ptr(), k.stride()
+    a.v, (a.v_sb, a.v_sh, a.v_sl, _) = v.data_ptr(), v.stride()
+    a.o, (a.o_sb, a.o_sh, a.o_sl, _) = o.data_ptr(), o.stride()
     a.wait_limit_ns = _lib.DEFAULT_WAIT_NS
-    a.sched_scratch = _sched_scratch(q.device).data_ptr()
+    dev = q.get_device()
+    stream = _raw_stream(dev)
+    a.sched_scratch = _sched_scratch(dev, stream, q.device)
+    return stream
 
 
 _SCRATCH = {}
 
 
-def _sched_scratch(device: torch.device) -> torch.Tensor:
-    """Work counter of the persistent attention kernels: two zeroed int32 per (device, stream).  The
-    kernels leave the counter at zero, so it is allocated and cleared only once."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
-    buf = _SCRATCH.get(key)
+def _sched_scratch(dev: int, stream: int, device: torch.device) -> int:
+    """Work counter of the persistent attention kernels: two zeroed int32 per (device, stream), returned as a
+    device address.  The kernels leave the counter at zero, so it is allocated and cleared only once."""
+    buf = _SCRATCH.get((dev, stream))
     if buf is None:
         buf = torch.zeros(2, dtype=torch.int32, device=device)
-        _SCRATCH[key] = buf
-    return buf
+        _SCRATCH[(dev, stream)] = buf
+    return buf.data_ptr()
 
 
 def new_status(device) -> torch.Tensor:
@@ -82,7 +86,7 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
     B, H, Lq, _ = q.shape
     M = L = None
     a = AttnArgs()
-    _fill_qkv(a, q, k, v, o, scale)
+    stream = _fill_qkv(a, q, k, v, o, scale)
     if return_stats:
         M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
         L = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
@@ -91,7 +95,7 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
         a.dev_status = status.data_ptr()
     if wait_limit_ns is not None:
         a.wait_limit_ns = int(wait_limit_ns)
-    check(lib.lvar_dense_attn(C.byref(a), _stream_ptr(q.device)))
+    check(lib.lvar_dense_attn(C.byref(a), stream))
     return o, M, L
 
 
@@ -105,7 +109,7 @@ def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=Non
     Lkv = k.shape[2]
     cs = torch.empty((B, H, (Lq + 127) // 128, Lkv), dtype=torch.float32, device=q.device)
     a = AttnArgs()
-    _fill_qkv(a, q, k, v, o, scale)
+    stream = _fill_qkv(a, q, k, v, o, scale)
     a.cs, a.cs_sb, a.cs_sh, a.cs_st = cs.data_ptr(), cs.stride(0), cs.stride(1), cs.stride(2)
     M = L = None
     if return_stats:
@@ -114,7 +118,7 @@ def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=Non
         a.M, a.L = M.data_ptr(), L.data_ptr()
     if status is not None:
         a.dev_status = status.data_ptr()
-    check(lib.lvar_dense_colsum_attn(C.byref(a), _stream_ptr(q.device)))
+    check(lib.lvar_dense_colsum_attn(C.byref(a), stream))
     return (o, cs, M, L) if return_stats else (o, cs)
 
 
@@ -135,7 +139,8 @@ def colsum_tiles_fwd(q, k, scale=None, *, stats=None, return_stats=False, status
     a.q, a.q_sb, a.q_sh, a.q_sl = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
     a.k, a.k_sb, a.k_sh, a.k_sl = k.data_ptr(), k.stride(0), k.stride(1), k.stride(2)
     a.wait_limit_ns = _lib.DEFAULT_WAIT_NS
-    a.sched_scratch = _sched_scratch(q.device).data_ptr()
+    stream = _raw_stream(q.get_device())
+    a.sched_scratch = _sched_scratch(q.get_device(), stream, q.device)
     a.cs, a.cs_sb, a.cs_sh, a.cs_st = cs.data_ptr(), cs.stride(0), cs.stride(1), cs.stride(2)
     M = L = None
     if stats is not None:
@@ -150,7 +155,7 @@ def colsum_tiles_fwd(q, k, scale=None, *, stats=None, return_stats=False, status
         a.M, a.L = M.data_ptr(), L.data_ptr()
     if status is not None:
         a.dev_status = status.data_ptr()
-    check(lib.lvar_colsum_tiles(C.byref(a), 1 if stats is not None else 0, _stream_ptr(q.device)))
+    check(lib.lvar_colsum_tiles(C.byref(a), 1 if stats is not None else 0, stream))
     return (cs, M, L) if return_stats else cs
 
 
@@ -201,7 +206,7 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
         m = m.contiguous()
     o = torch.empty_like(q, memory_format=torch.contiguous_format)
     a = AttnArgs()
-    _fill_qkv(a, q, k, v, o, scale)
+    stream = _fill_qkv(a, q, k, v, o, scale)
     a.block_mask = m.data_ptr()
     a.bm_sb = m.stride(0) if m.shape[0] > 1 else 0
     a.bm_sh = m.stride(1) if m.shape[1] > 1 else 0
@@ -214,7 +219,7 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
         a.M, a.L = M.data_ptr(), L.data_ptr()
     if status is not None:
         a.dev_status = status.data_ptr()
-    check(lib.lvar_block_sparse_attn(C.byref(a), _stream_ptr(q.device)))
+    check(lib.lvar_block_sparse_attn(C.byref(a), stream))
     return (o, M, L) if return_stats else o
 
 
@@ -247,7 +252,7 @@ def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None
         raise RuntimeError("Output shape mismatch - o: {}, q: {}".format(tuple(o_in.shape), tuple(q.shape)))
     o = torch.empty_like(q, memory_format=torch.contiguous_format) if out is None else out
     a = AttnArgs()
-    _fill_qkv(a, q, k, v, o, scale)
+    stream = _fill_qkv(a, q, k, v, o, scale)
     a.o_in_side, a.o_side = int(resize_from), side
     a.indices = indices.data_ptr()
     a.i_sb, a.i_sh, a.i_sg = indices.stride(0), indices.stride(1), indices.stride(2)
@@ -259,7 +264,7 @@ def csp_attn_fwd(q, k, v, indices, counts, o_in, o_scale, group_rows, scale=None
     a.o_scale = int(o_scale)
     if status is not None:
         a.dev_status = status.data_ptr()
-    check(lib.lvar_csp_attn(C.byref(a), _stream_ptr(q.device)))
+    check(lib.lvar_csp_attn(C.byref(a), stream))
     return o
 
 
