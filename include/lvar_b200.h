@@ -60,6 +60,10 @@ typedef struct lvar_attn_args {
    * elements (innermost 1) */
   float* cs;
   int64_t cs_sb, cs_sh, cs_st;
+  /* 1 (also when 0): one row of cs per 128-row query tile.  2: one row per 256-row group,
+   * fp32 [B,H,ceil(Lq/256),Lkv]; the caller zeroes cs first and the group's two tiles add into the row
+   * (two addends onto zero: the same bits in either order). */
+  int32_t cs_group_tiles;
   /* block-sparse only: uint8 mask [*, *, ceil(Lq/bs), ceil(Lkv/bs)], nonzero = attend, bs = block_size.
    * A stride of 0 broadcasts over batch / head. Innermost stride is 1. */
   const uint8_t* block_mask;

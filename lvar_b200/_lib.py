@@ -44,6 +44,7 @@ class AttnArgs(C.Structure):
         ("o", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sl", C.c_int64),
         ("M", C.c_void_p), ("L", C.c_void_p),
         ("cs", C.c_void_p), ("cs_sb", C.c_int64), ("cs_sh", C.c_int64), ("cs_st", C.c_int64),
+        ("cs_group_tiles", C.c_int32),
         ("block_mask", C.c_void_p), ("bm_sb", C.c_int64), ("bm_sh", C.c_int64), ("bm_sq", C.c_int64),
         ("block_size", C.c_int32),
         ("indices", C.c_void_p), ("i_sb", C.c_int64), ("i_sh", C.c_int64), ("i_sg", C.c_int64),

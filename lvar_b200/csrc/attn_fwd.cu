@@ -72,6 +72,7 @@ struct AttnParams {
   float* L;  // [B,H,Lq] or nullptr
   float* cs;  // MODE_DENSE_CS / MODE_CS_ONLY: column sums per 128-row query tile [B,H,ceil(Lq/128),Lkv]
   int64_t cs_sb, cs_sh, cs_st;
+  int cs_pair;  // 1: the two 128-row tiles of a 256-row group add into ONE zero-initialised row of cs
   const float* M_in;  // MODE_CS_ONLY: row statistics supplied by the caller (both or neither); the
   const float* L_in;  // statistics sweep is then skipped
   // block mask (MODE_BLOCK): uint8 [*,*,nqb,nkb], broadcast over batch/head when the stride is 0
@@ -514,7 +515,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool full_tile = im.row_end[s] - im.row0[s] >= 128;
         const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
         const int tile = im.row0[s] >> 7;
-        float* cs_row = p.cs + im.b * p.cs_sb + im.h * p.cs_sh + (int64_t)tile * p.cs_st;
+        float* cs_row = p.cs + im.b * p.cs_sb + im.h * p.cs_sh + (int64_t)(p.cs_pair ? tile >> 1 : tile) * p.cs_st;
         // the sweep over the KV tiles, compiled twice: the exponential mix is a compile-time choice (a run-time
         // choice per chunk measured 20 % slower)
         auto cs_sweep = [&](auto poly_tag) -> bool {
@@ -539,7 +540,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_fence_before();
             mbar_arrive(&bars->cs_empty[s][buf]);
             const int key = j * 128 + r_in_tile;
-            if (key < p.Lkv) cs_row[key] = acc;
+            if (key < p.Lkv) {
+              // two addends onto zero give the same bits in either order
+              if (p.cs_pair) atomicAdd(cs_row + key, acc);
+              else cs_row[key] = acc;
+            }
           }
           return true;
         };
@@ -1093,6 +1098,9 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     p.cs_sb = a->cs_sb;
     p.cs_sh = a->cs_sh;
     p.cs_st = a->cs_st;
+    LVAR_REQUIRE(a->cs_group_tiles == 0 || a->cs_group_tiles == 1 || a->cs_group_tiles == 2, LVAR_ERR_ARG,
+                 "cs_group_tiles must be 1 (a row per 128-row tile) or 2 (a row per 256-row group)");
+    p.cs_pair = a->cs_group_tiles == 2 ? 1 : 0;
   }
   p.nkb = (a->Lkv + 127) / 128;
   p.status = a->dev_status;

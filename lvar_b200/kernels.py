@@ -99,18 +99,24 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
     return o, M, L
 
 
-def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=None):
-    """Dense attention plus, in the same launch, the attention column sums of every 128-row query tile:
-    returns (o, cs128) with cs128 fp32 [B,H,ceil(Lq/128),Lkv] (and M, L with return_stats)."""
+def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=None, group_tiles=1):
+    """Dense attention plus, in the same launch, the attention column sums of every 128-row query tile
+    (``group_tiles`` = 1) or of every 256-row group (2): returns (o, cs) with cs fp32
+    [B,H,ceil(Lq/(128*group_tiles)),Lkv] (and M, L with return_stats)."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
+    if group_tiles not in (1, 2):
+        raise RuntimeError("group_tiles must be 1 or 2")
     o = torch.empty_like(q, memory_format=torch.contiguous_format)
     B, H, Lq, _ = q.shape
     Lkv = k.shape[2]
-    cs = torch.empty((B, H, (Lq + 127) // 128, Lkv), dtype=torch.float32, device=q.device)
+    rows = 128 * group_tiles
+    cs = (torch.zeros if group_tiles == 2 else torch.empty)((B, H, (Lq + rows - 1) // rows, Lkv),
+                                                            dtype=torch.float32, device=q.device)
     a = AttnArgs()
     stream = _fill_qkv(a, q, k, v, o, scale)
     a.cs, a.cs_sb, a.cs_sh, a.cs_st = cs.data_ptr(), cs.stride(0), cs.stride(1), cs.stride(2)
+    a.cs_group_tiles = group_tiles
     M = L = None
     if return_stats:
         M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)

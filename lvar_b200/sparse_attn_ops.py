@@ -38,8 +38,11 @@ def _dense_colsum(q, k, v, scale):
     if pad_to % 128 == 0:
         # one launch: the attention kernel sweeps the K tiles a second time for the column sums of its 128-row
         # query tiles; a group of pad_to rows is pad_to / 128 adjacent tiles, added in a fixed order
-        o, cs128 = K.dense_colsum_attn_fwd(q, k, v, scale)
-        cs = K.sum_tiles(cs128, pad_to // 128)
+        if pad_to == 256:  # a work item of the kernel is exactly one group: its two tiles add into one row
+            o, cs = K.dense_colsum_attn_fwd(q, k, v, scale, group_tiles=2)
+        else:
+            o, cs128 = K.dense_colsum_attn_fwd(q, k, v, scale)
+            cs = K.sum_tiles(cs128, pad_to // 128)
     else:
         o, M, L = K.dense_attn_fwd(q, k, v, scale)
         cs = K.colsum_fwd(q, k, M, L, pad_to, scale)

@@ -262,6 +262,11 @@ def test_fused_dense_colsum_matches_separate_kernels_and_oracle(K, B, H, Lq, Lkv
     # twice in a row on the same stream: the work counter and every barrier phase start over cleanly
     o2, cs2 = K.dense_colsum_attn_fwd(qc, kc, vc)
     assert torch.equal(o2, o) and torch.equal(cs2, cs)
+    # one row per 256-row group: the group's two tiles add into the row inside the launch, same bits as adding
+    # the per-tile rows afterwards (odd tile counts leave the last group with one tile)
+    o3, cs256 = K.dense_colsum_attn_fwd(qc, kc, vc, group_tiles=2)
+    assert torch.equal(o3, o) and cs256.shape == (B, H, (Lq + 255) // 256, Lkv)
+    assert torch.equal(cs256, K.sum_tiles(cs, 2))
 
 
 @pytest.mark.parametrize("B,H,Lq,Lkv,D", [(1, 2, 700, 900, 64), (2, 3, 1000, 1300, 128), (1, 1, 100, 77, 128),
