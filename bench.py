@@ -482,7 +482,7 @@ def run_ours(args):
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel<128, block-sparse> launch on this
 # workload, from the ncu capture summarised in profiles/ 
 PRE_ROLL = 8  # untimed steps queued between the synchronize and the start event of the timed region
-TRAFFIC_BYTES_PER_LAUNCH = 187.5e6  # 165.9 MB read + 21.6 MB written (profiles/attn_fwd_block_sparse_c2.md)
+TRAFFIC_BYTES_PER_LAUNCH = 186.5e6  # 166.5 MB read + 20.0 MB written (profiles/attn_fwd_block_sparse_c2.md)
 
 
 def main():
