@@ -221,7 +221,9 @@ def make_prologue(ref: Path) -> dict:
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/Lvar")
+    ref = Path(sys.argv[1])
     _install_stubs(ref)
     ref_ops = importlib.import_module("kernels.sparse_attn.sparse_attn_ops")
     ref_colsum = importlib.import_module("kernels.sparse_attn.triton.attn_dense_colsum")
