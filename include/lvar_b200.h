@@ -86,14 +86,25 @@ typedef struct lvar_attn_args {
   /* scheduling: the kernels are persistent (one CTA per SM) and draw work items from a counter in
    * device memory.  sched_scratch points to TWO int32 that are zero when the kernel starts; the kernel
    * leaves them zero, so one zeroed buffer serves every later launch on the same stream.  Launches
-   * that may overlap on the GPU need separate buffers.  work_order (optional, int32[work items]) is
-   * the order in which items are handed out, e.g. heaviest first. */
+   * that may overlap on the GPU need separate buffers.
+   * A work item is a PAIR of adjacent 128-row query tiles of one (batch, head): pair id =
+   * (b * H + h) * ceil(Lq / 256) + pair index (column-sparse: groups of group_rows rows take the place of
+   * Lq).  work_order (optional, device int32[B * H * pairs per head]) is a permutation of the pair ids: the
+   * pair at position i is handed out i-th, e.g. heaviest first for a ragged block mask.  When the last wave
+   * of pairs fills at most half of the SMs, the pairs at the END of the order are handed out as single
+   * tiles; dense and block-sparse attention run such a tile on both halves of the CTA, each half taking
+   * half of the tile's KV blocks, and merge the two partial results in the epilogue. */
   int32_t* sched_scratch;
   const int32_t* work_order;
   /* plumbing */
   int32_t* dev_status;    /* optional device int32, must be zeroed by the caller; see LVAR_DEV_* */
   uint64_t wait_limit_ns; /* per-wait limit of the kernel's bounded waits; 0 forces every pending wait to fail */
+  /* scheduling switches (0 = default; for measurements and tests): LVAR_SCHED_* bits */
+  int32_t sched_flags;
 } lvar_attn_args;
+
+#define LVAR_SCHED_PAIRS_ONLY 1     /* never hand the last wave out as single tiles */
+#define LVAR_SCHED_SINGLE_ONE_SLOT 2 /* a single tile runs on one half of the CTA (no KV split, no merge) */
 
 /* Dense attention o = softmax(q k^T * scale) v with row statistics.
  * Replaces torch.ops.chipmunk.dense_attn (kernels/chipmunk/csrc/attn/dense_attn.cu:248-372) and

@@ -22,6 +22,7 @@ DEV_STATUS_NAMES = {
     6: "forced timeout (wait limit 0)",
 }
 DEFAULT_WAIT_NS = 2_000_000_000
+SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT = 1, 2  # lvar_attn_args.sched_flags
 
 
 class LvarError(RuntimeError):
@@ -55,6 +56,7 @@ class AttnArgs(C.Structure):
         ("sched_scratch", C.c_void_p), ("work_order", C.c_void_p),
         ("dev_status", C.c_void_p),
         ("wait_limit_ns", C.c_uint64),
+        ("sched_flags", C.c_int32),
     ]
 
 

@@ -101,8 +101,9 @@ struct AttnParams {
   int n_x;            // query-tile pairs per (batch, head)
   int n_pair_items;   // items [0, n_pair_items) are pairs, [n_pair_items, total_items) single tiles
   int total_items;
+  int split_singles;  // 1: a single-tile item runs on BOTH slots, each taking half of the tile's KV list
   int* sched_counter;  // device int32[2], zero on entry and left zero on exit
-  const int32_t* work_order;  // optional permutation of the work items (heaviest first)
+  const int32_t* work_order;  // optional permutation of the pair items: schedule position -> pair (heaviest first)
   // plumbing
   int* status;
   unsigned long long wait_limit_ns;
@@ -119,15 +120,18 @@ struct Smem {
   static constexpr int kBarBytes = 512;
   static constexpr int kList = kAux + kBarBytes;
   static constexpr int kNegC = kList + kSchedStages * 2 * kMaxSteps * 2;    // [slot][128] fp32: -(M_i + log2 L_i)
-  static constexpr int kTotal = kNegC + 2 * 128 * 4;
+  static constexpr int kXchg = kNegC + 2 * 128 * 4;  // [item parity][m_ref, l, m_true][128] fp32: slot 1 -> slot 0 of a split tile
+  static constexpr int kTotal = kXchg + 2 * 3 * 128 * 4;
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
 struct SchedEntry {
-  int item;  // work item id, < 0: no more work
+  int item;  // pair id, < 0: no more work
+  int half;  // < 0: the whole pair; 0 / 1: only that 128-row tile of the pair
   int n0;    // KV tiles of slot 0
   int n1;    // KV tiles of slot 1
   int aux;   // csp: length of the item's index list
+  int off1;  // dense, split tile: slot 1 starts at this KV tile (slot 0 takes the tiles before it)
 };
 
 // One round of the two slots' tile streams: slot s works on KV tile kvb[s] if has[s]; when both want
@@ -145,6 +149,7 @@ struct Bars {
   uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
   uint64_t sched_full[kSchedStages], sched_empty[kSchedStages];
   uint64_t mma_done;
+  uint64_t xchg_full[2];  // split tile: slot 1's partial result is complete (128 arrivals), by item parity
   // column-sum sweep (MODE_DENSE_CS): S^T of a slot is double-buffered, [slot][buffer]
   uint64_t cs_full[2][2], cs_empty[2][2];
   SchedEntry sched[kSchedStages];
@@ -174,6 +179,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   Bars* bars = reinterpret_cast<Bars*>(smem + SM::kAux);
   uint16_t* lists = reinterpret_cast<uint16_t*>(smem + SM::kList);  // [kSchedStages][kMaxSteps]
   float* negc = reinterpret_cast<float*>(smem + SM::kNegC);
+  float* xchg = reinterpret_cast<float*>(smem + SM::kXchg);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -204,6 +210,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&bars->sched_empty[i], 11);  // 8 softmax warps + K loader + V loader + MMA issuer
     }
     mbar_init(&bars->mma_done, 1);
+    mbar_init(&bars->xchg_full[0], 128);
+    mbar_init(&bars->xchg_full[1], 128);
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -223,27 +231,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = bars->tmem_base;
   WaitCtx wc{p.status, &bars->abort_flag, p.wait_limit_ns};
 
-  // A work item is one (batch, head) x (pair of 128-row query tiles).  Decoded by every role itself.
+  // A work item is one (batch, head) x (pair of 128-row query tiles), or one tile of such a pair.  Decoded by
+  // every role itself.
   struct Item {
     int b, h, bh, group;
     int row0[2], row_end[2];
     uint32_t live;  // bit s: slot s has at least one query row
+    bool split;     // both slots work on the SAME query tile, each on its own part of the tile's KV list
   };
-  // Items below p.n_pair_items are pairs of query tiles; the rest are the single tiles of the last,
-  // partial wave of pairs (see launch_attention), which run with slot 1 idle.
-  auto decode = [&](int item) {
+  // The pairs of the last, partial wave are handed out as single tiles (see launch_attention).  A single tile
+  // either runs on slot 0 with slot 1 idle, or (p.split_singles) on both slots: the slots then hold the same
+  // query rows, walk disjoint halves of the KV list and slot 0's softmax warps merge the two partial results,
+  // which halves the length of the tile's dependent QK -> softmax -> PV chain.
+  auto decode = [&](int item, int half) {
     Item it;
-    int half = -1;
-    if (item >= p.n_pair_items) {
-      const int tile = 2 * p.n_pair_items + (item - p.n_pair_items);
-      half = tile & 1;
-      item = tile >> 1;
-    }
     it.bh = item / p.n_x;
     const int x = item % p.n_x;
     it.b = it.bh / p.H;
     it.h = it.bh % p.H;
     it.group = 0;
+    it.split = false;
     int gend = p.Lq;
     if (MODE == MODE_CSP) {
       it.group = x / p.chunks_per_group;
@@ -255,9 +262,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     it.row0[1] = it.row0[0] + 128;
     it.row_end[0] = it.row_end[1] = gend;
-    if (half >= 0) {  // single tile: slot 0 takes it, slot 1 stays empty
+    if (half >= 0) {
       it.row0[0] += half * 128;
-      it.row0[1] = gend;
+      it.split = p.split_singles != 0;
+      it.row0[1] = it.split ? it.row0[0] : gend;  // not split: slot 0 takes the tile, slot 1 stays empty
     }
     it.live = (it.row0[0] < gend ? 1u : 0u) | (it.row0[1] < gend ? 2u : 0u);
     return it;
@@ -270,7 +278,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       rd.kvb[0] = rd.has[0] ? (l0[r] & 0xFFF) : 0;
       rd.kvb[1] = rd.has[1] ? (l1[r] & 0xFFF) : 0;
     } else {
-      rd.kvb[0] = rd.kvb[1] = r;
+      rd.kvb[0] = r;
+      rd.kvb[1] = r + e.off1;
     }
     rd.shared = rd.has[0] && rd.has[1] && rd.kvb[0] == rd.kvb[1];
     return rd;
@@ -304,13 +313,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int n_s = 0;  // S tiles consumed by this slot so far (parity of s_full)
     int n_o = 0;  // items in which this slot produced an output (parity of o_full)
     int n_cs[2] = {0, 0};  // column-sum sweep: S^T tiles read per buffer (parity of cs_full)
+    int n_xc[2] = {0, 0};  // split tiles merged so far, by item parity (parity of xchg_full)
     bool ok = true;
 
     for (int n = 0; ok; ++n) {
       SchedEntry e;
       ok = __all_sync(0xffffffffu, acquire_item(n, e, DEV_TIMEOUT_SOFTMAX));
       if (!ok || e.item < 0) break;
-      const Item im = decode(e.item);
+      const Item im = decode(e.item, e.half);
       const uint16_t* mylist = lists + ((n % kSchedStages) * 2 + s) * kMaxSteps;
       const int row = im.row0[s] + r_in_tile;
       const bool row_ok = row < im.row_end[s];
@@ -321,7 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       int it = 0;
       const int n_first = stats_given ? 0 : n_mine;
       for (int j = 0; j < n_first; ++j) {
-        const int kvb = (MODE == MODE_BLOCK) ? (mylist[j] & 0xFFF) : j;
+        const int kvb = (MODE == MODE_BLOCK) ? (mylist[j] & 0xFFF) : j + (s == 1 ? e.off1 : 0);
         const uint32_t sub = (MODE == MODE_BLOCK) ? ((uint32_t)mylist[j] >> 12 >> (2 * (r_in_tile >> 6))) & 3u : 3u;
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, wc, DEV_TIMEOUT_SOFTMAX));
         if (!ok) break;  // warp-uniform: the TMEM accesses below are warp-collective
@@ -424,6 +434,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;
 
       // ---- epilogue: O / l -> bf16 -> global; row statistics
+      const bool split = (MODE == MODE_DENSE || MODE == MODE_BLOCK) && im.split;
+      float m_stat = m_true, l_stat = (it > 0 && l > 0.f) ? l * fast_exp2(m_ref - m_true) : 0.f;
       if (MODE != MODE_CS_ONLY) {
         if (it > 0) {
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, wc, DEV_TIMEOUT_SOFTMAX));
@@ -431,65 +443,107 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ++n_o;
           tc_fence_after();
         }
-        const float inv_l = (it > 0 && l > 0.f) ? (1.0f / l) : 0.f;
-        __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
-        const __nv_bfloat16* irow =
-            (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
-        // accumulate input taken from a coarser token grid: this row's four source tokens and weights
-        const bool resize = (MODE == MODE_CSP) && p.oi_side > 0;
-        BilinearTaps tp = {};
-        const __nv_bfloat16* ibase = nullptr;
-        if (resize && row_ok) {
-          tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
-          ibase = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
-        }
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          if (it > 0) {
-            tmem_ld_x32(tO + c * 32, r);
-            tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
+        if (split && s == 1) {
+          // Second half of a split tile: hand this row's reference maximum, denominator and true maximum to
+          // slot 0's warpgroup, which reads both accumulators out of TMEM and merges them.
+          float* x = xchg + (n & 1) * 3 * 128;
+          x[r_in_tile] = (it > 0) ? m_ref : -INFINITY;
+          x[128 + r_in_tile] = (it > 0) ? l : 0.f;
+          x[256 + r_in_tile] = m_true;
+          tc_fence_before();
+          mbar_arrive(&bars->xchg_full[n & 1]);
+        } else {
+          float w0 = (it > 0 && l > 0.f) ? (1.0f / l) : 0.f, w1 = 0.f;  // out = O_0 * w0 + O_1 * w1
+          bool other = false;  // slot 1 holds a partial result of this tile
+          if (split) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->xchg_full[n & 1], n_xc[n & 1] & 1, wc, DEV_TIMEOUT_SOFTMAX));
+            if (!ok) break;
+            ++n_xc[n & 1];
+            tc_fence_after();
+            const float* x = xchg + (n & 1) * 3 * 128;
+            const float m1 = x[r_in_tile], l1 = x[128 + r_in_tile], mt1 = x[256 + r_in_tile];
+            other = e.n1 > 0;
+            const float m0 = (it > 0) ? m_ref : -INFINITY;
+            const float mm = fmaxf(m0, m1);
+            const float a0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mm);
+            const float a1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mm);
+            const float lt = a0 * l + a1 * l1;
+            const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+            w0 = a0 * inv;
+            w1 = a1 * inv;
+            m_stat = fmaxf(m_true, mt1);
+            l_stat = lt > 0.f ? lt * fast_exp2(mm - m_stat) : 0.f;
           }
-          if (c == D / 32 - 1 && it > 0) {
-            // O has been read out of TMEM: the MMA warp may overwrite it for the next item
-            tc_fence_before();
-            mbar_arrive(&bars->o_empty[s]);
+          const uint32_t tO1 = tmem_base + lane_off + TM_O + (uint32_t)D;  // slot 1's accumulator (split tiles)
+          __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
+          const __nv_bfloat16* irow =
+              (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
+          // accumulate input taken from a coarser token grid: this row's four source tokens and weights
+          const bool resize = (MODE == MODE_CSP) && p.oi_side > 0;
+          BilinearTaps tp = {};
+          const __nv_bfloat16* ibase = nullptr;
+          if (resize && row_ok) {
+            tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
+            ibase = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
           }
-          if (row_ok) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint32_t w[4];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            if (it > 0) {
+              tmem_ld_x32(tO + c * 32, r);
+              tmem_wait_ld();
+            } else {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float x0 = __uint_as_float(r[q4 * 8 + 2 * i]) * inv_l;
-                const float x1 = __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l;
-                w[i] = pack_bf16x2(x0, x1);
-              }
-              if (MODE == MODE_CSP) {
-                // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
-                // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
-                uint4 prev;
-                if (resize) {
-                  const __nv_bfloat16* ib = ibase + c * 32 + q4 * 8;
-                  prev = bilinear_mix8(tp, *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r00 * p.oi_sl),
-                                       *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r01 * p.oi_sl),
-                                       *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r10 * p.oi_sl),
-                                       *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r11 * p.oi_sl));
-                } else {
-                  prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (split && other) {
+              uint32_t r1[32];
+              tmem_ld_x32(tO1 + c * 32, r1);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                r[i] = __float_as_uint(fmaf(__uint_as_float(r1[i]), w1, __uint_as_float(r[i]) * w0));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * w0);
+            }
+            if (c == D / 32 - 1) {
+              // O has been read out of TMEM: the MMA warp may overwrite it for the next item.  For a split tile
+              // this warpgroup read slot 1's accumulator too and releases it in its owner's stead.
+              tc_fence_before();
+              if (it > 0) mbar_arrive(&bars->o_empty[s]);
+              if (split && other) mbar_arrive(&bars->o_empty[1]);
+            }
+            if (row_ok) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  w[i] = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2 * i]), __uint_as_float(r[q4 * 8 + 2 * i + 1]));
+                if (MODE == MODE_CSP) {
+                  // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
+                  // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
+                  uint4 prev;
+                  if (resize) {
+                    const __nv_bfloat16* ib = ibase + c * 32 + q4 * 8;
+                    prev = bilinear_mix8(tp, *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r00 * p.oi_sl),
+                                         *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r01 * p.oi_sl),
+                                         *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r10 * p.oi_sl),
+                                         *reinterpret_cast<const uint4*>(ib + (int64_t)tp.r11 * p.oi_sl));
+                  } else {
+                    prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
+                  }
+                  const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float d0 = __uint_as_float(w[i] << 16), d1 = __uint_as_float(w[i] & 0xffff0000u);
+                    const float a0 = __uint_as_float(pv[i] << 16), a1 = __uint_as_float(pv[i] & 0xffff0000u);
+                    w[i] = pack_bf16x2(fmaf(p.o_scale, d0, a0), fmaf(p.o_scale, d1, a1));
+                  }
                 }
-                const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float d0 = __uint_as_float(w[i] << 16), d1 = __uint_as_float(w[i] & 0xffff0000u);
-                  const float a0 = __uint_as_float(pv[i] << 16), a1 = __uint_as_float(pv[i] & 0xffff0000u);
-                  w[i] = pack_bf16x2(fmaf(p.o_scale, d0, a0), fmaf(p.o_scale, d1, a1));
-                }
+                *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
               }
-              *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
         }
@@ -499,10 +553,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int64_t si = (int64_t)im.bh * p.Lq + row;
         m_ref = row_ok ? p.M_in[si] : -INFINITY;
         l = row_ok ? p.L_in[si] : 0.f;
-      } else if (row_ok && MODE != MODE_CSP) {
+      } else if (row_ok && MODE != MODE_CSP && !(split && s == 1)) {
         const int64_t si = (int64_t)im.bh * p.Lq + row;
-        if (p.M) p.M[si] = m_true;
-        if (p.L) p.L[si] = (it > 0 && l > 0.f) ? l * fast_exp2(m_ref - m_true) : 0.f;
+        if (p.M) p.M[si] = m_stat;
+        if (p.L) p.L[si] = l_stat;
       }
       if (kHasCs && n_mine > 0) {
         // ---- second sweep: column sums of this slot's query tile.  S^T = K Q^T lands in S_s with one KEY per
@@ -569,7 +623,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = acquire_item(n, e, DEV_TIMEOUT_PRODUCER);
         if (MODE == MODE_CSP) ok = __all_sync(0xffffffffu, ok);
         if (!ok || e.item < 0) break;
-        const Item im = decode(e.item);
+        const Item im = decode(e.item, e.half);
         const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
         const uint16_t* l1 = l0 + kMaxSteps;
         const int rounds = max(e.n0, e.n1);
@@ -665,7 +719,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = acquire_item(n, e, DEV_TIMEOUT_PRODUCER);
         if (MODE == MODE_CSP) ok = __all_sync(0xffffffffu, ok);
         if (!ok || e.item < 0) break;
-        const Item im = decode(e.item);
+        const Item im = decode(e.item, e.half);
         const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
         const uint16_t* l1 = l0 + kMaxSteps;
         const int rounds = max(e.n0, e.n1);
@@ -748,7 +802,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         SchedEntry e;
         ok = acquire_item(n, e, DEV_TIMEOUT_MMA);
         if (!ok || e.item < 0) break;
-        const Item im = decode(e.item);
+        const Item im = decode(e.item, e.half);
         const uint16_t* l0 = lists + ((n % kSchedStages) * 2) * kMaxSteps;
         const uint16_t* l1 = l0 + kMaxSteps;
         const int rounds = max(e.n0, e.n1);
@@ -919,18 +973,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = __all_sync(0xffffffffu,
                       mbar_wait(&bars->sched_empty[slot], ((n / kSchedStages) & 1) ^ 1, wc, DEV_TIMEOUT_PRODUCER));
       if (!ok) break;
-      int item = -1;
+      int item = -1, half = -1;
       if (lane == 0) {
         const int idx = atomicAdd(p.sched_counter, 1);
-        if (idx < p.total_items) item = p.work_order ? p.work_order[idx] : idx;
+        if (idx < p.total_items) {
+          // schedule positions [0, n_pair_items) are whole pairs; the rest are the two tiles of each later pair
+          int pos = idx;
+          if (idx >= p.n_pair_items) {
+            const int tile = 2 * p.n_pair_items + (idx - p.n_pair_items);
+            pos = tile >> 1;
+            half = tile & 1;
+          }
+          item = p.work_order ? p.work_order[pos] : pos;
+        }
       }
       item = __shfl_sync(0xffffffffu, item, 0);
-      int n0 = 0, n1 = 0, aux = 0;
+      half = __shfl_sync(0xffffffffu, half, 0);
+      int n0 = 0, n1 = 0, aux = 0, off1 = 0;
       if (item >= 0) {
-        const Item im = decode(item);
+        const Item im = decode(item, half);
         // The item's Q tiles are read once in the whole launch, so they come from HBM, and their load sits
         // between two items with nothing to overlap it: start them towards L2 now, one item ahead.
-        if (lane < 2 * NSUB && ((im.live >> (lane / NSUB)) & 1u))
+        if (lane < 2 * NSUB && ((im.live >> (lane / NSUB)) & 1u) && !(im.split && lane >= NSUB))
           tma_prefetch_l2_4d(&tmQ, (lane % NSUB) * 64, lane < NSUB ? im.row0[0] : im.row0[1], im.h, im.b);
         uint16_t* l0 = lists + (slot * 2) * kMaxSteps;
         uint16_t* l1 = l0 + kMaxSteps;
@@ -956,12 +1020,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const int qt0 = im.row0[0] >> 7, qt1 = im.row0[1] >> 7;
           // Tiles that both slots want come first, in the same positions of both lists, so that they are
           // loaded once (a round shares a tile when both lists name it at the same position); the tiles
-          // only one slot wants follow.  Ascending within each class.
+          // only one slot wants follow.  Ascending within each class.  A split tile has one list (slot 0's).
           for (int pass = 0; pass < 2; ++pass) {
             for (int base = 0; base < p.nkb; base += 32) {
               const int j = base + lane;
               uint32_t b0 = (j < p.nkb && (im.live & 1u)) ? sub_bits(qt0, j) : 0u;
-              uint32_t b1 = (j < p.nkb && (im.live & 2u)) ? sub_bits(qt1, j) : 0u;
+              uint32_t b1 = (j < p.nkb && (im.live & 2u) && !im.split) ? sub_bits(qt1, j) : 0u;
               const bool both = b0 != 0 && b1 != 0;
               if (both != (pass == 0)) b0 = b1 = 0u;
               const uint32_t v0 = __ballot_sync(0xffffffffu, b0 != 0), v1 = __ballot_sync(0xffffffffu, b1 != 0);
@@ -974,6 +1038,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           n0 = min(n0, kMaxSteps);
           n1 = min(n1, kMaxSteps);
+          if (im.split) {
+            // slot 0 keeps the first half of the tile's list, slot 1 gets the rest
+            const int all = n0;
+            n0 = (all + 1) / 2;
+            n1 = all - n0;
+            __syncwarp();
+            for (int i = lane; i < n1; i += 32) l1[i] = l0[n0 + i];
+          }
         } else {
           int n = p.nkb;
           if (MODE == MODE_CSP) {
@@ -982,11 +1054,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           n0 = (im.live & 1u) ? n : 0;
           n1 = (im.live & 2u) ? n : 0;
+          if (im.split && n0 > 0) {
+            n0 = (n + 1) / 2;
+            n1 = n - n0;
+            off1 = n0;
+          }
         }
       }
       __syncwarp();
       if (lane == 0) {
         bars->sched[slot].item = item;
+        bars->sched[slot].half = half;
+        bars->sched[slot].off1 = off1;
         bars->sched[slot].n0 = n0;
         bars->sched[slot].n1 = n1;
         bars->sched[slot].aux = aux;
@@ -1176,17 +1255,20 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   LVAR_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   p.n_pair_items = (int)total;
   p.total_items = (int)total;
-  if (mode != MODE_CSP && total > sms) {
+  // A single tile of the attention modes runs on both slots, each taking half of the tile's KV list
+  // (see the kernel's decode); the column-sum modes keep one slot idle instead.
+  p.split_singles = ((mode == MODE_DENSE || mode == MODE_BLOCK) && !(a->sched_flags & LVAR_SCHED_SINGLE_ONE_SLOT)) ? 1 : 0;
+  if (mode != MODE_CSP && (total > sms || p.split_singles) && !(a->sched_flags & LVAR_SCHED_PAIRS_ONLY)) {
     // Wave quantisation: the pairs left over after the last full wave of CTAs are handed out as single
     // query tiles when those fit in one wave, so that the tail costs one short item per CTA instead of
-    // one full pair on a few CTAs.
+    // one full pair on a few CTAs.  With work_order the tail is the end of the caller's order.
     const int64_t rem = total % sms;
     if (rem > 0 && 2 * rem <= sms) {
       p.n_pair_items = (int)(total - rem);
       p.total_items = (int)(total + rem);
     }
   }
-  dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
+  dim3 grid((unsigned)(p.total_items < sms ? p.total_items : sms), 1, 1);
 
   CUtensorMap tq, tk, tv;
   int rc = encode_bhld_map(&tq, a->q, a->B, a->H, a->Lq, a->D, a->q_sb, a->q_sh, a->q_sl, 128);

@@ -18,6 +18,8 @@
 //     Two calls that may overlap on the GPU (different streams, no ordering) race on it: do not.
 //   * The first call on each device looks the array's device address up (cudaGetSymbolAddress) and
 //     sets kernel attributes; make that first call outside any stream capture.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace lvar {
@@ -39,7 +41,11 @@ constexpr size_t kScratchBytes = kCounterBytes + 2 * kStatBytes;
 static __device__ __align__(256) unsigned char g_static_scratch[kScratchBytes];
 
 constexpr int kMaxDevices = 64;
-unsigned char* g_scratch_addr[kMaxDevices] = {nullptr};
+// Per device: the looked-up address, published with release/acquire so that two host threads making their
+// first call at the same time agree (both look the same address up; either store wins).  The address stays
+// valid for the life of the device's primary context: a cudaDeviceReset unloads the library's module, and a
+// host that resets a device must not call this entry point on it again in the same process.
+std::atomic<unsigned char*> g_scratch_addr[kMaxDevices];
 
 // Device address of the scratch on the current device; looked up once per device.
 int scratch_base(unsigned char** out) {
@@ -47,15 +53,17 @@ int scratch_base(unsigned char** out) {
   LVAR_CUDA_OK(cudaGetDevice(&dev));
   LVAR_REQUIRE(dev >= 0 && dev < kMaxDevices, LVAR_ERR_LIMIT, "device ordinal %d not supported (max %d)", dev,
                kMaxDevices - 1);
-  if (g_scratch_addr[dev] == nullptr) {
+  unsigned char* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess || ptr == nullptr)
       return fail(LVAR_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed on device %d: %s", dev,
                   cudaGetErrorString(e));
-    g_scratch_addr[dev] = static_cast<unsigned char*>(ptr);
+    addr = static_cast<unsigned char*>(ptr);
+    g_scratch_addr[dev].store(addr, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = addr;
   return LVAR_OK;
 }
 

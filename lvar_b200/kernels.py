@@ -78,7 +78,7 @@ def read_status(status: torch.Tensor) -> Tuple[int, str]:
     return code, _lib.DEV_STATUS_NAMES.get(code, f"unknown status {code}")
 
 
-def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None):
+def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None, sched_flags=0):
     """o = softmax(q k^T * scale) v; returns (o, M, L) with fp32 [B,H,Lq] statistics in base 2."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
@@ -95,6 +95,7 @@ def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_
         a.dev_status = status.data_ptr()
     if wait_limit_ns is not None:
         a.wait_limit_ns = int(wait_limit_ns)
+    a.sched_flags = int(sched_flags)
     check(lib.lvar_dense_attn(C.byref(a), stream))
     return o, M, L
 
@@ -189,8 +190,35 @@ def colsum_groups_fwd(q, k, M, L, group_rows, scale=None):
     return colsum_fwd(q, k, M, L, group_rows, scale)
 
 
-def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None, block=128):
-    """Attention under a block mask of 128x128 (or 64x64) blocks: uint8/bool [nq,nk], [H,nq,nk] or [B,H,nq,nk]."""
+def heaviest_first_order(block_mask: torch.Tensor, B: int, H: int, block: int = 128) -> torch.Tensor:
+    """Schedule order for a ragged block mask: the ids of the kernel's work items (pairs of 128-row query tiles,
+    id = (b * H + h) * pairs_per_head + pair) sorted by their number of active KV tiles, heaviest first (ties by
+    id), as int32 on the mask's device.  ``block_mask`` is [nq,nk], [H,nq,nk] or [B,H,nq,nk].  Build it once
+    per mask (it runs a sort) and pass it as ``work_order``."""
+    m = block_mask
+    while m.dim() < 4:
+        m = m.unsqueeze(0)
+    nq, nk = m.shape[-2:]
+    m = m.to(torch.bool)
+    if block == 64:  # a 128-row tile is two mask rows, a 128-key tile two mask columns
+        if nk % 2:
+            m = torch.nn.functional.pad(m, (0, 1))
+        m = m.view(*m.shape[:-1], -1, 2).any(-1)
+        if nq % 2:
+            m = torch.nn.functional.pad(m, (0, 0, 0, 1))
+        m = m.view(*m.shape[:-2], -1, 2, m.shape[-1]).any(-2)
+    tiles = m.sum(-1, dtype=torch.int32)                       # active KV tiles per 128-row query tile
+    if tiles.shape[-1] % 2:
+        tiles = torch.nn.functional.pad(tiles, (0, 1))
+    pairs = tiles.view(*tiles.shape[:-1], -1, 2).sum(-1)       # [*, *, pairs_per_head]
+    pairs = pairs.expand(B, H, pairs.shape[-1]).reshape(-1)
+    return torch.sort(pairs, descending=True, stable=True).indices.to(torch.int32)
+
+
+def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None, block=128,
+                          work_order=None, sched_flags=0):
+    """Attention under a block mask of 128x128 (or 64x64) blocks: uint8/bool [nq,nk], [H,nq,nk] or [B,H,nq,nk].
+    ``work_order``: optional int32 permutation of the work items (see :func:`heaviest_first_order`)."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
     B, H, Lq, _ = q.shape
@@ -218,6 +246,12 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
     a.bm_sh = m.stride(1) if m.shape[1] > 1 else 0
     a.bm_sq = m.stride(2)
     a.block_size = int(block)
+    if work_order is not None:
+        n_items = B * H * ((Lq + 255) // 256)
+        if (work_order.dtype != torch.int32 or work_order.device != q.device or work_order.numel() != n_items
+                or not work_order.is_contiguous()):
+            raise RuntimeError(f"work_order must be a contiguous int32 tensor of {n_items} work item ids on {q.device}")
+        a.work_order = work_order.data_ptr()
     M = L = None
     if return_stats:
         M = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
@@ -225,6 +259,7 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
         a.M, a.L = M.data_ptr(), L.data_ptr()
     if status is not None:
         a.dev_status = status.data_ptr()
+    a.sched_flags = int(sched_flags)
     check(lib.lvar_block_sparse_attn(C.byref(a), stream))
     return (o, M, L) if return_stats else o
 

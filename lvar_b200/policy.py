@@ -306,11 +306,22 @@ class SparseFlexAttn:
         self.block_size = block_size
         self.block_mask_cpu = csla_block_mask(scale_schedule, kernel_schedule, q_scale_idx, attn_sink_scale, block_size)
         self.block_mask = self.block_mask_cpu.to(device) if torch.cuda.is_available() else None
+        self._orders: Dict[tuple, torch.Tensor] = {}
+
+    def _order(self, B: int, H: int, device) -> torch.Tensor:
+        """The mask is static and ragged (the window widens with the key scale), so the kernel's work items are
+        handed out heaviest first; the order depends on (B, H) only and is built once."""
+        key = (B, H, str(device))
+        if key not in self._orders:
+            self._orders[key] = K.heaviest_first_order(self.block_mask, B, H, self.block_size)
+        return self._orders[key]
 
     def forward(self, q, k, v, scale=None):
         from .sparse_attn_ops import block_sparse_attn
         if self.block_mask is None or self.block_mask.device != q.device:
             self.block_mask = self.block_mask_cpu.to(q.device)
-        return block_sparse_attn(q.to(v.dtype), k.to(v.dtype), v, self.block_mask, scale, self.block_size)
+            self._orders.clear()
+        return block_sparse_attn(q.to(v.dtype), k.to(v.dtype), v, self.block_mask, scale, self.block_size,
+                                 work_order=self._order(q.shape[0], q.shape[1], q.device))
 
     __call__ = forward

@@ -112,11 +112,12 @@ def csp_attn_resized(q, k, v, scale, indices, indices_counts, o_cache, o_scale):
     return K.csp_attn_fwd(q, k, v, indices, indices_counts, o_cache, int(o_scale), bm, scale, resize_from=side)
 
 
-def block_sparse_attn(q, k, v, block_mask, scale=None, block_size=128):
+def block_sparse_attn(q, k, v, block_mask, scale=None, block_size=128, work_order=None):
     """Attention under a block mask of 128x128 (or 64x64) blocks ([nq,nk], [H,nq,nk] or [B,H,nq,nk], bool); the kernel
     behind ``SparseFlexAttn.forward`` in this package, standing in for
-    ``flex_attention(q, k, v, block_mask=...)`` (models/sparvar/basic_sparvar.py:187-194)."""
-    return K.block_sparse_attn_fwd(q, k, v, block_mask, scale, block=block_size)
+    ``flex_attention(q, k, v, block_mask=...)`` (models/sparvar/basic_sparvar.py:187-194).  ``work_order``
+    (``kernels.heaviest_first_order``) hands the query tiles of a ragged mask out heaviest first."""
+    return K.block_sparse_attn_fwd(q, k, v, block_mask, scale, block=block_size, work_order=work_order)
 
 
 def bitpack(mask: torch.Tensor):

@@ -39,6 +39,16 @@ def _check_o(o_gpu, o_ref):
     assert d.mean().item() <= O_MEAN, f"mean-abs {d.mean().item():.3e}"
 
 
+def _cs_rel(cs, ref):
+    """Largest ELEMENT-WISE relative error of column sums against the fp64 oracle.  Sums below 1e-30 (the
+    probability mass of a whole group on a key the peaked rows never look at) are compared absolutely."""
+    ref = ref.double()
+    return ((cs.double().cpu() - ref).abs() / ref.abs().clamp_min(1e-30)).max().item()
+
+
+SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT = 1, 2  # lvar_attn_args.sched_flags
+
+
 def _ok_status(K, st):
     code, text = K.read_status(st)
     assert code == 0, text
@@ -247,18 +257,23 @@ def test_fused_dense_colsum_matches_separate_kernels_and_oracle(K, B, H, Lq, Lkv
     bit for bit, the sums agree with the stand-alone column-sum kernel and with the fp64 oracle, ragged tiles
     and the single-tile tail items included."""
     from oracle import attention as oa
-    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq)
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq, peaked=True)
     qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
     st = K.new_status("cuda")
     o, cs, M, L = K.dense_colsum_attn_fwd(qc, kc, vc, return_stats=True, status=st)
     _ok_status(K, st)
-    dense, M0, L0 = K.dense_attn_fwd(qc, kc, vc)
+    # the same schedule (single tiles on one half of the CTA) gives the dense kernel's bits; the default dense
+    # schedule splits a single tile's keys over both halves and agrees to rounding
+    dense, M0, L0 = K.dense_attn_fwd(qc, kc, vc, sched_flags=SCHED_SINGLE_ONE_SLOT)
     assert torch.equal(o, dense) and torch.equal(M, M0) and torch.equal(L, L0)
+    dense_s, M1, L1 = K.dense_attn_fwd(qc, kc, vc)
+    assert (dense_s.float() - dense.float()).abs().max().item() <= 1.6e-2  # one bf16 ulp at |o| < 4
+    assert torch.allclose(M1, M0, rtol=1e-6, atol=1e-6) and torch.allclose(L1, L0, rtol=1e-5)
     sep = K.colsum_fwd(qc, kc, M0, L0, 128)
     assert cs.shape == sep.shape == (B, H, (Lq + 127) // 128, Lkv)
     assert ((cs - sep).abs() <= 1e-5 * sep.abs().max()).all()
     _, ref = oa.dense_colsum_attn(q, k, v, None, q_group_size=128, dtype=torch.float64)
-    assert ((cs.cpu().double() - ref.double()).abs().max() / ref.double().abs().max()).item() <= CS_REL
+    assert _cs_rel(cs, ref) <= CS_REL
     # twice in a row on the same stream: the work counter and every barrier phase start over cleanly
     o2, cs2 = K.dense_colsum_attn_fwd(qc, kc, vc)
     assert torch.equal(o2, o) and torch.equal(cs2, cs)
@@ -276,7 +291,7 @@ def test_colsum_tiles_without_output_matches_fused_launch(K, B, H, Lq, Lkv, D):
     statistics are the fused attention + column-sum launch's bit for bit; with the statistics supplied by the
     caller only the second sweep runs and agrees to rounding.  More work items than SMs in the last case."""
     from oracle import attention as oa
-    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq + 1)
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq + 1, peaked=True)
     qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
     _, want, M0, L0 = K.dense_colsum_attn_fwd(qc, kc, vc, return_stats=True)
     st = K.new_status("cuda")
@@ -290,7 +305,8 @@ def test_colsum_tiles_without_output_matches_fused_launch(K, B, H, Lq, Lkv, D):
     assert torch.equal(K.colsum_tiles_fwd(qc, kc), cs)  # back to back on one stream
     if B * H <= 6:
         _, ref = oa.dense_colsum_attn(q, k, v, None, q_group_size=128, dtype=torch.float64)
-        assert ((cs.cpu().double() - ref.double()).abs().max() / ref.double().abs().max()).item() <= CS_REL
+        assert _cs_rel(cs, ref) <= CS_REL
+        assert _cs_rel(cs2, ref) <= CS_REL
 
 
 def test_colsum_groups_from_given_stats_and_argument_checks(K):
@@ -441,3 +457,84 @@ def test_full_size_properties(K):
     a1 = K.block_sparse_attn_fwd(q[:1], k[:1], v[:1], ones, scale)
     a2 = K.block_sparse_attn_fwd(q[:1], k[:1], (v[:1].float() * 2).bfloat16(), ones, scale)
     assert torch.equal(a2.float(), a1.float() * 2)
+
+
+# ----------------------------------------------------------------------------------------------
+# scheduling variants: single tiles split over both halves of a CTA, caller-supplied work order
+# ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("B,H,Lq,Lkv,D", [(1, 1, 100, 77, 128), (1, 3, 700, 1500, 128), (2, 2, 300, 1000, 64),
+                                          (1, 1, 256, 128, 128), (2, 40, 512, 640, 64), (2, 45, 512, 900, 128)])
+def test_split_single_tiles_agree_with_pairs_and_oracle(K, B, H, Lq, Lkv, D):
+    """A single query tile of the last wave runs on both halves of the CTA, each half on half of the keys, and
+    the partial results are merged in the epilogue: same result (to rounding) as the pair schedule and as single
+    tiles on one half, for dense and block-sparse attention, row statistics included.  Odd tile counts, one
+    tile (nothing for the second half) and more items than SMs are covered."""
+    from oracle import attention as oa
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=Lq + Lkv + 7, peaked=True)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    st = K.new_status("cuda")
+    o, M, L = K.dense_attn_fwd(qc, kc, vc, status=st)
+    _ok_status(K, st)
+    for flags in (SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT):
+        o2, M2, L2 = K.dense_attn_fwd(qc, kc, vc, sched_flags=flags)
+        assert (o.float() - o2.float()).abs().max().item() <= 1.6e-2
+        assert torch.allclose(M, M2, rtol=1e-6, atol=1e-6) and torch.allclose(L, L2, rtol=1e-5)
+    if B * H <= 6:
+        o_ref, M_ref, L_ref = oa.dense_attn(q, k, v)
+        _check_o(o, o_ref)
+        assert torch.allclose(M.cpu(), M_ref, atol=1e-4, rtol=1e-4) and torch.allclose(L.cpu(), L_ref, rtol=1e-4)
+    nq, nk = (Lq + 127) // 128, (Lkv + 127) // 128
+    g = torch.Generator().manual_seed(Lq)
+    bm = torch.rand(B, H, nq, nk, generator=g) < 0.5
+    bm[..., 0] = True
+    bm[0, 0, -1] = False
+    bmc = bm.cuda()
+    st = K.new_status("cuda")
+    ob, Mb, Lb = K.block_sparse_attn_fwd(qc, kc, vc, bmc, return_stats=True, status=st)
+    _ok_status(K, st)
+    ob2, Mb2, Lb2 = K.block_sparse_attn_fwd(qc, kc, vc, bmc, return_stats=True, sched_flags=SCHED_PAIRS_ONLY)
+    assert (ob.float() - ob2.float()).abs().max().item() <= 1.6e-2
+    assert torch.allclose(Mb, Mb2, rtol=1e-6, atol=1e-6) and torch.allclose(Lb, Lb2, rtol=1e-5)
+    assert torch.equal(ob, K.block_sparse_attn_fwd(qc, kc, vc, bmc))  # bit-reproducible
+    if B * H <= 6:
+        _check_o(ob, oa.block_sparse_attn(q, k, v, bm))
+
+
+def test_work_order_heaviest_first(K):
+    """A caller-supplied order of the work items changes when a query tile runs, not what it computes: with the
+    pair schedule the output is bit-identical, with the default schedule (the END of the order runs as single
+    tiles) it agrees to rounding.  The order is a permutation sorted by active KV tiles."""
+    from lvar_b200 import policy as P
+    from oracle import attention as oa
+    scales = P.INFINITY_SCALES
+    mask = P.csla_block_mask([(s, s) for s in scales], [-1] * 8 + [1, 1, 3, 5, 7], 11, 5).cuda()
+    B, H, Lq, Lkv, D = 2, 12, 2304, 6425, 128
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=31)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    order = K.heaviest_first_order(mask, B, H)
+    n_items = B * H * ((Lq + 255) // 256)
+    assert order.dtype == torch.int32 and sorted(order.tolist()) == list(range(n_items))
+    tiles = mask.sum(-1)
+    per_pair = (tiles[0::2] + torch.nn.functional.pad(tiles[1::2], (0, tiles[0::2].numel() - tiles[1::2].numel())))
+    w = per_pair[(order.long() % per_pair.numel())]
+    assert (w[:-1] >= w[1:]).all(), "heaviest first"
+    plain = K.block_sparse_attn_fwd(qc, kc, vc, mask, sched_flags=SCHED_PAIRS_ONLY)
+    st = K.new_status("cuda")
+    ordered = K.block_sparse_attn_fwd(qc, kc, vc, mask, work_order=order, sched_flags=SCHED_PAIRS_ONLY, status=st)
+    _ok_status(K, st)
+    assert torch.equal(plain, ordered)
+    st = K.new_status("cuda")
+    default = K.block_sparse_attn_fwd(qc, kc, vc, mask, work_order=order, status=st)
+    _ok_status(K, st)
+    assert (default.float() - plain.float()).abs().max().item() <= 1.6e-2
+    _check_o(default[:1, :2], oa.block_sparse_attn(q[:1, :2], k[:1, :2], v[:1, :2], mask.cpu()))
+    # 64-wide masks: the order counts 128-wide tiles
+    m64 = torch.rand(Lq // 64, (Lkv + 63) // 64, generator=torch.Generator().manual_seed(2)) < 0.2
+    m64[:, 0] = True
+    o64 = K.heaviest_first_order(m64.cuda(), B, H, block=64)
+    assert sorted(o64.tolist()) == list(range(n_items))
+    a = K.block_sparse_attn_fwd(qc, kc, vc, m64.cuda(), block=64, sched_flags=SCHED_PAIRS_ONLY)
+    b = K.block_sparse_attn_fwd(qc, kc, vc, m64.cuda(), block=64, work_order=o64, sched_flags=SCHED_PAIRS_ONLY)
+    assert torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        K.block_sparse_attn_fwd(qc, kc, vc, mask, work_order=order[:-1].contiguous())

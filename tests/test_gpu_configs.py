@@ -96,5 +96,8 @@ def test_2048px_style_last_scale_window_plus_topk(K):
         d = (o[b, h, rows].float() - ref).abs()
         assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
     # keeping every block reproduces dense attention bit for bit
+    # (same work-item schedule on both sides: one head each)
     ones = torch.ones(nq, nk, dtype=torch.bool, device="cuda")
-    assert torch.equal(K.block_sparse_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], ones, scale), o_d[:1, :1])
+    d1, _, _ = K.dense_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], scale)
+    assert torch.equal(K.block_sparse_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], ones, scale), d1)
+    assert (d1.float() - o_d[:1, :1].float()).abs().max().item() <= 1.6e-2

@@ -5,7 +5,9 @@ they run under a no-allocation-after-warm-up rule where a cudaMalloc per layer i
 stall the device.  For them the library keeps the intermediate row statistics and the attention
 kernel's work counter in a device array of its own.  This test calls that entry point twice in a row
 (the second call reuses the array with the first call's leftovers in it) and compares both results
-with the ordinary entry points lvar_dense_attn + lvar_colsum, which take caller-allocated buffers.
+with the ordinary entry points lvar_dense_attn + lvar_colsum, which take caller-allocated buffers, and
+with the CPU oracle; around the second call it also checks that neither the driver's free memory nor
+torch's allocator moved.
 It is collected last so that a failure here cannot hide any other test under `pytest -x`.
 """
 import ctypes as C
@@ -37,19 +39,39 @@ def test_static_entry_point_matches_allocating_path_twice():
     from lvar_b200 import _lib
     from lvar_b200 import kernels as K
     lib = _lib.lib
+    from oracle import attention as oa
     g = torch.Generator().manual_seed(2024)
     # two different problems back to back: the second one finds the first one's statistics in the array
-    for (B, H, Lq, Lkv, D, bm) in [(2, 4, 700, 1300, 128, 256), (1, 3, 333, 900, 64, 192)]:
-        q, k, v = (torch.randn(B, H, n, D, generator=g).bfloat16().cuda() for n in (Lq, Lkv, Lkv))
+    # (and a third call with the second one's shape, whose kernels are loaded by then, for the allocation check)
+    for call, (B, H, Lq, Lkv, D, bm) in enumerate([(2, 4, 700, 1300, 128, 256), (1, 3, 333, 900, 64, 192),
+                                                   (1, 3, 333, 900, 64, 192)]):
+        q_h, k_h, v_h = (torch.randn(B, H, n, D, generator=g).bfloat16() for n in (Lq, Lkv, Lkv))
+        q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
         scale = 1.0 / math.sqrt(D)
         G = (Lq + bm - 1) // bm
         o = torch.full((B, H, Lq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
         cs = torch.full((B, H, G, Lkv), float("nan"), dtype=torch.float32, device="cuda")
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        stats_before = torch.cuda.memory_stats()
         rc = _call_static(lib, q, k, v, o, cs, bm, scale, status)
         assert rc == 0, lib.lvar_last_error().decode()
         torch.cuda.synchronize()
+        if call == 2:
+            # the first launch of a kernel may load its code (module memory); after that nothing moves
+            assert torch.cuda.mem_get_info()[0] == free_before, "driver free memory changed across the call"
+            stats_after = torch.cuda.memory_stats()
+            for key in ("allocation.all.allocated", "segment.all.allocated", "num_device_alloc"):
+                assert stats_after.get(key, 0) == stats_before.get(key, 0), f"torch allocator moved: {key}"
         assert int(status.item()) == 0
+
+        # against the CPU oracle (fp32 output bar, element-wise column-sum bar)
+        o_cpu, cs_cpu = oa.dense_colsum_attn(q_h, k_h, v_h, scale, q_group_size=bm, dtype=torch.float64)
+        d = (o.float().cpu() - o_cpu.float()).abs()
+        assert d.max().item() <= O_MAX and d.mean().item() <= O_MEAN
+        rel = ((cs.double().cpu() - cs_cpu).abs() / cs_cpu.abs().clamp_min(1e-30)).max().item()
+        assert rel <= CS_REL, f"column sums differ from the oracle: {rel:.3e}"
 
         o_ref, M, L = K.dense_attn_fwd(q, k, v, scale)
         cs_ref = K.colsum_fwd(q, k, M, L, bm, scale)
