@@ -53,6 +53,19 @@ def group_remap_table(n_target: int, n_source: int) -> torch.Tensor:
 
 def local_band(scales: Sequence[int], scale_ind: int, win: int, bm: int, counts_multiple_of: int
                ) -> Tuple[torch.Tensor, int]:
+    """See :func:`_local_band`; results are cached (every layer of a model asks for the same tables)."""
+    key = (tuple(scales), scale_ind, win, bm, counts_multiple_of)
+    if key not in _BAND_CACHE:
+        _BAND_CACHE[key] = _local_band(scales, scale_ind, win, bm, counts_multiple_of)
+    band, length = _BAND_CACHE[key]
+    return band.clone(), length
+
+
+_BAND_CACHE: Dict[tuple, Tuple[torch.Tensor, int]] = {}
+
+
+def _local_band(scales: Sequence[int], scale_ind: int, win: int, bm: int, counts_multiple_of: int
+                ) -> Tuple[torch.Tensor, int]:
     """Static local prior of one scale: for each group of ``bm`` queries a contiguous run of KV
     indices that starts at the smallest key any of its queries sees through a clamp-padded
     ``win x win`` window on the scale's own grid; all runs share one length (the largest group union
@@ -133,16 +146,6 @@ def sink_local_blocks(nq: int, nk: int, block: int, sink_tokens: int, q_offset: 
     b0 = lo // block - window_blocks
     b1 = hi // block + window_blocks
     return (j < (sink_tokens + block - 1) // block) | ((j >= b0) & (j <= b1))
-
-
-def upsample_ocache(o_cache: torch.Tensor, L_src: int, L_tgt: int) -> torch.Tensor:
-    """Bilinear (align_corners=False) resize of an output cache [B,H,L_src,D] viewed as a square grid
-    (sparse_attn.py:324-362)."""
-    B, H, _, Dh = o_cache.shape
-    s, t = int(L_src ** 0.5), int(L_tgt ** 0.5)
-    grid = o_cache.view(B * H, s, s, Dh).permute(0, 3, 1, 2)
-    grid = F.interpolate(grid, size=(t, t), mode="bilinear", align_corners=False)
-    return grid.permute(0, 2, 3, 1).reshape(B, H, t * t, Dh)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -323,5 +326,76 @@ class SparseFlexAttn:
             self._orders.clear()
         return block_sparse_attn(q.to(v.dtype), k.to(v.dtype), v, self.block_mask, scale, self.block_size,
                                  work_order=self._order(q.shape[0], q.shape[1], q.device))
+
+    __call__ = forward
+
+
+# --------------------------------------------------------------------------------------------------
+# which attention runs for (scale, layer)
+# --------------------------------------------------------------------------------------------------
+def build_csla_list(scales: Sequence[int] = tuple(INFINITY_SCALES), attn_config: Optional[dict] = None,
+                    num_heads: int = 16, block_size: int = 128, device="cuda") -> List[Optional[SparseFlexAttn]]:
+    """One entry per scale: ``None`` below the decision scale, a :class:`SparseFlexAttn` from it on (the
+    ``spattn_compile_list`` of models/sparvar/sparvar_model.py:275-318, whose three modules are the scales from
+    ``decision_scale`` to the last)."""
+    cfg = GLOBAL_CONFIG["attn"] if attn_config is None else attn_config
+    sched = [(s, s) for s in scales]
+    win = list(cfg["win_size"])
+    assert len(win) == len(scales), f"kernel_schedule mismatch {len(scales)} scales"
+    first = cfg["decision_scale"]
+    return [None if si < first else
+            SparseFlexAttn(sched, win, q_scale_idx=si, attn_sink_scale=cfg["attn_sink"], block_size=block_size,
+                           num_heads=num_heads, device=device)
+            for si in range(len(scales))]
+
+
+class SelfAttentionDispatch:
+    """The attention call of one transformer layer during generation: picks, per (scale, layer), what
+    ``SelfAttention.forward`` picks in models/sparvar/basic_sparvar.py:353-387 -
+
+    * ``layer_ind > bound_layer`` and a static-mask module is given for the scale (scales from the decision
+      scale on): sink + local-window block-sparse attention ("csla");
+    * ``scale_ind == decision_scale`` and ``layer_ind <= bound_layer``: dense attention + column sums + top-k,
+      O-cache ("cs4a_full");
+    * ``scale_ind > decision_scale`` and ``layer_ind <= bound_layer``: column-sparse delta attention on the
+      stored lists ("cs4a_sparse");
+    * everything else: dense attention ("dense"; the reference calls ``torch.ops.chipmunk.dense_attn`` there).
+
+    q, k, v are bf16 [B,H,L,D] (k, v: the whole KV cache up to this scale); returns o bf16 [B,H,Lq,D]."""
+
+    def __init__(self, layer_ind: int, attn_config: Optional[dict] = None, scales: Sequence[int] = tuple(INFINITY_SCALES),
+                 scale: float = 1.0, layer_counter: Optional[LayerCounter] = None):
+        cfg = GLOBAL_CONFIG["attn"] if attn_config is None else attn_config
+        self.layer_ind = layer_ind
+        self.spsd_scale = cfg["decision_scale"]
+        self.bound_layer = cfg["bound_layer"]
+        self.scale = scale
+        self.last_route: Optional[str] = None
+        n_sparse = len(scales) - (self.spsd_scale + 1)
+        ws = list(cfg.get("cs4a_ws", [1] * 11 + [7, 9]))
+        self.sparse_attn = SparseDiffAttn(layer_ind, layer_counter, use_o_cache=True, scales=scales,
+                                          spsd_scale=self.spsd_scale, wind_size=ws[len(ws) - n_sparse:] if n_sparse else [],
+                                          speedup=bool(cfg.get("speedup", 0)), top_keys=cfg["top_keys"])
+
+    def route(self, scale_ind: int, layer_ind: Optional[int] = None, spattn_fn=None) -> str:
+        layer = self.layer_ind if layer_ind is None else layer_ind
+        if spattn_fn is not None and layer > self.bound_layer:
+            return "csla"
+        if scale_ind == self.spsd_scale and layer <= self.bound_layer:
+            return "cs4a_full"
+        if scale_ind > self.spsd_scale and layer <= self.bound_layer:
+            return "cs4a_sparse"
+        return "dense"
+
+    def forward(self, q, k, v, scale_ind: int = 0, layer_ind: Optional[int] = None, spattn_fn=None):
+        layer = self.layer_ind if layer_ind is None else layer_ind
+        r = self.last_route = self.route(scale_ind, layer, spattn_fn)
+        if r == "csla":
+            return spattn_fn(q, k, v, scale=self.scale)
+        if r == "cs4a_full":
+            return self.sparse_attn(q, k, v, scale=self.scale, do_full_step=True, scale_ind=scale_ind, layer_ind=layer)
+        if r == "cs4a_sparse":
+            return self.sparse_attn(q, k, v, scale=self.scale, scale_ind=scale_ind, layer_ind=layer)
+        return K.dense_attn_fwd(q, k, v, self.scale, return_stats=False)[0]
 
     __call__ = forward

@@ -6,7 +6,9 @@ One thing differs on purpose: there is a single backend.  ``attn.provider`` is s
 files written for the reference ('triton' or 'cuda'; 'b200' is accepted too) but it only gets
 validated; every value runs the sm_100a kernels of this package, and ``get_kernel_config_attn()``
 publishes THEIR tile geometry (callers such as the reference's SparseDiffAttn read it at run time,
-models/sparvar/sparse_attn.py:888-891,974-979).
+models/sparvar/sparse_attn.py:888-891,974-979).  The default geometry (256-row query groups, counts in
+multiples of 128) selects keys for different row groups than the reference's 192-row groups; set
+``GLOBAL_CONFIG['attn']['geometry'] = 'reference'`` to get the reference's groups and list lengths.
 """
 from __future__ import annotations
 
@@ -28,6 +30,12 @@ _ATTN = dict(
     first_n_dense_layers=2, full_step_every=10, full_step_schedule=None,
     recompute_mask=True, should_compress_indices=True, should_keep_tail_dense=False,
     provider="triton",
+    # CS4A / CSLA split and local-prior windows of models/sparvar/sparse-attn-config.yml
+    bound_layer=10, cs4a_ws=[1] * 11 + [7, 9],
+    # Tile geometry published by get_kernel_config_attn(): None = this library's own (256-row groups, counts in
+    # multiples of 128), "reference" = the geometry the reference publishes for the configured provider
+    # (192-row groups; counts in multiples of 64 for 'triton', 112 for 'cuda'), or a dict with the three keys.
+    geometry=None,
 )
 _OFFLOADING = {
     "global_disable_offloading": False,
@@ -75,9 +83,22 @@ def get_kernel_config_attn() -> Dict[str, int]:
     """Geometry of the attention kernels: ``bm`` query rows share one KV index list (and one colsum
     row), index counts are built as multiples of ``counts_multiple_of`` and index rows are padded to
     ``indices_pad_to`` entries.  Same keys as the reference (sparse_attn_config.py:82-98)."""
-    _check_provider()
+    provider = _check_provider()
     from ._lib import kernel_config_attn  # loads the CUDA library; raises if it is missing
-    return kernel_config_attn()
+    geo = kernel_config_attn()
+    override = GLOBAL_CONFIG["attn"].get("geometry")
+    if override is None or override == "b200":
+        return geo
+    if override == "reference":
+        # kernels/sparse_attn/sparse_attn_config.py:82-98
+        override = ({"bm": 192, "counts_multiple_of": 112, "indices_pad_to": 4} if provider == "cuda"
+                    else {"bm": 192, "counts_multiple_of": 64, "indices_pad_to": 1})
+    if not isinstance(override, dict) or set(override) - set(geo):
+        raise ValueError(f"attn.geometry must be None, 'b200', 'reference' or a dict with keys {sorted(geo)}")
+    geo.update({k: int(v) for k, v in override.items()})
+    if geo["bm"] < 32 or geo["bm"] % 32 or geo["counts_multiple_of"] < 1 or geo["indices_pad_to"] < 1:
+        raise ValueError(f"unsupported attention geometry {geo}: bm must be a positive multiple of 32")
+    return geo
 
 
 def update_global_config(config: Dict[str, Any]) -> None:

@@ -37,7 +37,9 @@ def test_dense_attn_and_colsum_return_conventions(ops):
         assert cs.shape == (2, 4, (600 + bm - 1) // bm, 900) and cs.dtype == torch.float32
         _, cs_ref = oa.dense_colsum_attn(q, k, v, 0.1, q_group_size=bm, dtype=torch.float64)
         assert ((cs.double().cpu() - cs_ref).abs() / cs_ref).max() <= 1e-3
-        assert torch.equal(o2, o)
+        # same attention, but the two launches may schedule their last tiles differently: equal to rounding
+        assert (o2.float() - o.float()).abs().max() <= 1.6e-2
+        assert (o2.float().cpu() - o_ref).abs().max() <= 2e-2
     # the materialising helper agrees with the kernels
     o3, cs3 = ops.naive_dense_colsum_attn(qc.float(), kc.float(), vc.float(), 0.1, q_group_size=bm)
     assert torch.allclose(cs3, cs, rtol=2e-3, atol=1e-6)

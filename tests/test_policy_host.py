@@ -55,11 +55,6 @@ def test_sink_local_blocks_matches_oracle():
         assert torch.equal(P.sink_local_blocks(*args), oi.sink_local_blocks(*args))
 
 
-def test_upsample_matches_golden(golden_indices):
-    out = P.upsample_ocache(golden_indices["upsample_in"], 36, 64)
-    assert torch.allclose(out, golden_indices["upsample_out"], atol=1e-6)
-
-
 def test_config_surface(tmp_path):
     assert set(cfg.BASE_CONFIG) >= {"attn", "mlp", "patchify", "offloading", "step_caching", "steps", "world_size"}
     assert cfg.GLOBAL_CONFIG["attn"]["win_size"] == [-1] * 8 + [1, 1, 3, 5, 7]
@@ -95,3 +90,72 @@ def test_sparse_diff_attn_tables():
         oband, ocount = oi.local_band(SCALES, s, {11: 7, 12: 9}[s], geo["bm"], geo["counts_multiple_of"])
         assert count == ocount and torch.equal(band.long(), oband)
         assert count % geo["counts_multiple_of"] == 0
+
+
+def test_dispatch_routes_follow_the_reference_branches():
+    """13 scales x 32 layers: the route is the branch SelfAttention.forward takes in
+    models/sparvar/basic_sparvar.py:353-387 with the yml's decision_scale 10 and bound_layer 10."""
+    attn_cfg = dict(cfg.GLOBAL_CONFIG["attn"], decision_scale=10, bound_layer=10, top_keys=0.2)
+    spattn = [None] * 10 + ["fn10", "fn11", "fn12"]  # spattn_compile_list: modules for the last three scales
+    layers = [P.SelfAttentionDispatch(li, attn_cfg) for li in (0, 10, 11, 31)]
+    counts = {}
+    for si in range(13):
+        for d in layers:
+            li = d.layer_ind
+            if spattn[si] is not None and li > 10:
+                want = "csla"
+            elif si == 10 and li <= 10:
+                want = "cs4a_full"
+            elif si > 10 and li <= 10:
+                want = "cs4a_sparse"
+            else:
+                want = "dense"
+            assert d.route(si, spattn_fn=spattn[si]) == want
+            counts[want] = counts.get(want, 0) + 1
+    assert counts == {"dense": 40, "cs4a_full": 2, "cs4a_sparse": 4, "csla": 6}
+    # without a static-mask module (flex attention switched off) the late layers stay dense
+    assert layers[-1].route(12, spattn_fn=None) == "dense"
+    # a layer's CS4A module is built for the configured decision scale and windows
+    assert sorted(layers[0].sparse_attn.local_inds) == [11, 12] and layers[0].sparse_attn.top_keys == 0.2
+
+
+def test_geometry_override():
+    saved = dict(cfg.GLOBAL_CONFIG["attn"])
+    try:
+        base = cfg.get_kernel_config_attn()
+        assert base == {"bm": 256, "counts_multiple_of": 128, "indices_pad_to": 4}
+        cfg.GLOBAL_CONFIG["attn"]["geometry"] = "reference"
+        cfg.GLOBAL_CONFIG["attn"]["provider"] = "triton"
+        assert cfg.get_kernel_config_attn() == {"bm": 192, "counts_multiple_of": 64, "indices_pad_to": 1}
+        cfg.GLOBAL_CONFIG["attn"]["provider"] = "cuda"
+        assert cfg.get_kernel_config_attn() == {"bm": 192, "counts_multiple_of": 112, "indices_pad_to": 4}
+        a = P.SparseDiffAttn(layer_num=0, top_keys=0.2)
+        assert (a.bm, a.multiple_of, a.indices_pad_to) == (192, 112, 4) and a.local_inds[11][1] == 560
+        cfg.GLOBAL_CONFIG["attn"]["geometry"] = {"bm": 128}
+        assert cfg.get_kernel_config_attn() == dict(base, bm=128)
+        for bad in ({"bm": 100}, {"rows": 3}, "fast"):
+            cfg.GLOBAL_CONFIG["attn"]["geometry"] = bad
+            try:
+                cfg.get_kernel_config_attn()
+                raise AssertionError("expected ValueError")
+            except ValueError:
+                pass
+    finally:
+        cfg.GLOBAL_CONFIG["attn"].clear()
+        cfg.GLOBAL_CONFIG["attn"].update(saved)
+
+
+def test_heaviest_first_order_host():
+    from lvar_b200 import kernels as K
+    mask = P.csla_block_mask([(s, s) for s in SCALES], WIN, 12, 5)          # [32, 83], ragged rows
+    order = K.heaviest_first_order(mask, 2, 3)
+    pairs = mask.sum(-1).view(16, 2).sum(-1)
+    assert order.dtype == torch.int32 and sorted(order.tolist()) == list(range(2 * 3 * 16))
+    w = pairs[order.long() % 16]
+    assert (w[:-1] >= w[1:]).all()
+    # per-(batch, head) masks and an odd number of query tiles
+    g = torch.Generator().manual_seed(0)
+    m = torch.rand(2, 3, 5, 9, generator=g) < 0.4
+    order = K.heaviest_first_order(m, 2, 3)
+    t = torch.nn.functional.pad(m.sum(-1), (0, 1)).view(2, 3, 3, 2).sum(-1).reshape(-1)
+    assert sorted(order.tolist()) == list(range(18)) and (t[order.long()][:-1] >= t[order.long()][1:]).all()
