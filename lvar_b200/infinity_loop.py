@@ -39,7 +39,9 @@ class LoopConfig:
     scales: Sequence[int] = field(default_factory=lambda: tuple(P.INFINITY_SCALES))
     cfg: float = 3.0                        # guidance strength on the logits
     tau: float = 1.0
-    sparse: bool = True                     # False: dense self-attention everywhere (the baseline model)
+    # "sparse": the per-(scale, layer) dispatch; "dense": dense self-attention everywhere (the baseline model);
+    # "none": the prologue still runs but no attention does (o = q) - for measuring self-attention's share
+    attn_mode: str = "sparse"
 
     @property
     def head_dim(self) -> int:
@@ -121,7 +123,9 @@ class InfinityLoop:
         self.v_cache = [torch.zeros_like(t) for t in self.k_cache]
         attn_cfg = GLOBAL_CONFIG["attn"]
         self.dispatch = [P.SelfAttentionDispatch(i, attn_cfg, cfg.scales, scale=1.0) for i in range(cfg.depth)]
-        self.csla = (P.build_csla_list(cfg.scales, attn_cfg, Hn, device=self.device) if cfg.sparse
+        if cfg.attn_mode not in ("sparse", "dense", "none"):
+            raise ValueError(f"attn_mode must be 'sparse', 'dense' or 'none', got {cfg.attn_mode!r}")
+        self.csla = (P.build_csla_list(cfg.scales, attn_cfg, Hn, device=self.device) if cfg.attn_mode == "sparse"
                      else [None] * len(cfg.scales))
         self.routes: Dict[str, int] = {}
         self._graph: Optional[torch.cuda.CUDAGraph] = None
@@ -137,11 +141,14 @@ class InfinityLoop:
         k = self.k_cache[li][:, :, :self.cum[si + 1]]
         v = self.v_cache[li][:, :, :self.cum[si + 1]]
         d = self.dispatch[li]
-        if cfg.sparse:
+        if cfg.attn_mode == "sparse":
             o = d(q, k, v, scale_ind=si, layer_ind=li, spattn_fn=self.csla[si])
-        else:
+        elif cfg.attn_mode == "dense":
             o = K.dense_attn_fwd(q, k, v, 1.0, return_stats=False)[0]
             d.last_route = "dense"
+        else:
+            o = q
+            d.last_route = "none"
         self.routes[d.last_route] = self.routes.get(d.last_route, 0) + 1
         return F.linear(o.transpose(1, 2).reshape(bs, L, C), blk.w_proj, blk.b_proj)
 

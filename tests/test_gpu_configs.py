@@ -101,3 +101,34 @@ def test_2048px_style_last_scale_window_plus_topk(K):
     d1, _, _ = K.dense_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], scale)
     assert torch.equal(K.block_sparse_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], ones, scale), d1)
     assert (d1.float() - o_d[:1, :1].float()).abs().max().item() <= 1.6e-2
+
+
+@pytest.mark.parametrize("variant", ["softmax_scale_1_over_sqrt_d", "cosine_attention_scale_1"])
+def test_benchmark_recipe_mask_and_output_match_the_oracle(K, variant):
+    """The headline workload of bench.py, built exactly as the bench builds it (fused attention + column sums ->
+    block scores -> sink <= 16x16 and own-position blocks -> top-k to 17 of 83 per row): the mask is the oracle's
+    bit for bit on the GPU's scores, the column sums agree element-wise, and the block-sparse output of four
+    sampled (batch, head) pairs is within max-abs 2e-2 / mean-abs 2e-3 of the oracle's dense masked fp32
+    attention.  Second variant: the cosine-attention form of the same tensors (unit-norm q and k, q scaled by 4,
+    softmax scale 1), which is what the model's self-attention feeds the kernel."""
+    import bench
+    from lvar_b200 import policy as P
+    from oracle import attention as oa
+    q, k, v = (t.cuda() for t in bench.make_inputs())
+    scale = 1.0 / math.sqrt(bench.D)
+    if variant == "cosine_attention_scale_1":
+        q, k = bench.cosine_variant(q, k)
+        scale = 1.0
+    mask, scores, always, cs, o_dense, M, L = bench.recipe_mask(K, P, q, k, v, scale)
+    assert mask.shape == (2, 16, 32, 83) and (mask.sum(-1) == bench.K_TOTAL).all()
+    assert (mask & always.cuda()).sum(-1).eq(always.sum(-1).cuda()).all(), "always-kept blocks are kept"
+    sample = [(0, 0), (0, 7), (1, 3), (1, 15)]
+    max_abs, mean_abs = bench.check_recipe_parity(K, q, k, v, scale, mask, scores, always, sample)
+    assert max_abs <= 2e-2 and mean_abs <= 2e-3
+    # the scores the mask is built from: column sums of two of the sampled heads, element-wise
+    for b, h in sample[:2]:
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        _, cs_ref = oa.dense_colsum_attn(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), scale, q_group_size=128,
+                                         dtype=torch.float64)
+        rel = ((cs[sl].double().cpu() - cs_ref).abs() / cs_ref.abs().clamp_min(1e-30)).max().item()
+        assert rel <= 1e-3, f"column sums of (b={b}, h={h}): {rel:.3e}"
