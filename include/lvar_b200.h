@@ -101,6 +101,10 @@ typedef struct lvar_attn_args {
   uint64_t wait_limit_ns; /* per-wait limit of the kernel's bounded waits; 0 forces every pending wait to fail */
   /* scheduling switches (0 = default; for measurements and tests): LVAR_SCHED_* bits */
   int32_t sched_flags;
+  /* lvar_dense_colsum_attn_given only: the row statistics to normalise with, fp32 [B,H,Lq] contiguous, in the
+   * convention of M and L above (as lvar_dense_attn writes them) */
+  const float* M_in;
+  const float* L_in;
 } lvar_attn_args;
 
 #define LVAR_SCHED_PAIRS_ONLY 1     /* never hand the last wave out as single tiles */
@@ -121,6 +125,20 @@ int lvar_dense_attn(const lvar_attn_args* args, lvar_stream_t stream);
  * separate column-sum kernel, kernels/sparse_attn/sparse_attn_ops.py:65-149,
  * kernels/sparse_attn/triton/attn_dense_colsum.py:101-296) when the group size is a multiple of 128. */
 int lvar_dense_colsum_attn(const lvar_attn_args* args, lvar_stream_t stream);
+
+/* Dense attention and its column sums in ONE sweep, for a caller that already holds the row statistics of this
+ * attention (args->M_in, args->L_in): every probability is formed once, already normalised,
+ *   p_ij = exp2(q_i.k_j * scale * log2e - M_in_i) / L_in_i,
+ * feeds both o = P v and cs[b,h,t,j] = sum over the rows i of tile t of p_ij (cs, cs_group_tiles as in
+ * lvar_dense_colsum_attn; fixed summation order, bit-reproducible).  o is divided by the measured row sums of p,
+ * so it is this attention's exact output also when the statistics come from another pass over slightly
+ * different data (they must be within a factor 2^100 of the true normaliser); the column sums are normalised by
+ * the GIVEN statistics, as in the reference.  args->M / args->L, when non-null, receive M_in and L_in times the
+ * row sum (the true statistics in the same convention).
+ * Replaces torch.ops.chipmunk.dense_colsum_attn(q, k, v, p) (kernels/chipmunk/csrc/attn/dense_colsum_attn.cu:
+ * 354-522; the column sums of the P tile it already holds for P V, :270-280), which the reference's
+ * dense_colsum_attn_s calls after dense_attn (kernels/sparse_attn/sparse_attn_ops.py:65-113). */
+int lvar_dense_colsum_attn_given(const lvar_attn_args* args, lvar_stream_t stream);
 
 /* The attention column sums alone, per 128-row query tile (cs as in lvar_dense_colsum_attn); v, o and their
  * strides are not read and may be null / 0.  stats_given = 0: one launch takes the row statistics in a first

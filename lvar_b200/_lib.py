@@ -57,6 +57,7 @@ class AttnArgs(C.Structure):
         ("dev_status", C.c_void_p),
         ("wait_limit_ns", C.c_uint64),
         ("sched_flags", C.c_int32),
+        ("M_in", C.c_void_p), ("L_in", C.c_void_p),
     ]
 
 
@@ -64,6 +65,7 @@ class AttnArgs(C.Structure):
 _SIGNATURES = {
     "lvar_dense_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_dense_colsum_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "lvar_dense_colsum_attn_given": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_colsum_tiles": (C.c_int, [C.POINTER(AttnArgs), C.c_int32, C.c_void_p]),
     "lvar_block_sparse_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "lvar_csp_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),

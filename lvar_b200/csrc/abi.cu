@@ -155,6 +155,10 @@ int lvar_dense_colsum_attn(const lvar_attn_args* args, lvar_stream_t stream) {
   return lvar::launch_attention(args, 3, static_cast<cudaStream_t>(stream));
 }
 
+int lvar_dense_colsum_attn_given(const lvar_attn_args* args, lvar_stream_t stream) {
+  return lvar::launch_attention(args, 6, static_cast<cudaStream_t>(stream));
+}
+
 int lvar_colsum_tiles(const lvar_attn_args* args, int32_t stats_given, lvar_stream_t stream) {
   return lvar::launch_attention(args, stats_given ? 5 : 4, static_cast<cudaStream_t>(stream));
 }

@@ -60,7 +60,13 @@ constexpr float kRescaleThreshold = 32.0f;
 // the attention column sums of the item's two query tiles (see the softmax warps).
 // MODE_CS_ONLY: the column sums alone.  The first sweep only takes the row statistics (no P, no PV, no V
 // loads, no output), or is left out when the caller supplies them; the second sweep is MODE_DENSE_CS's.
-enum AttnMode : int { MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2, MODE_DENSE_CS = 3, MODE_CS_ONLY = 4 };
+// MODE_DENSE_CS1: dense attention and the column sums in ONE sweep, for callers that supply the row statistics
+// (the form of the reference's CUDA operator, kernels/chipmunk/csrc/attn/dense_colsum_attn.cu:270-280): the
+// probabilities that feed P V are normalised with the given constants as they are formed, and their column
+// sums are taken from the same registers.  (5 is launch_attention's code for MODE_CS_ONLY on given statistics.)
+enum AttnMode : int {
+  MODE_DENSE = 0, MODE_BLOCK = 1, MODE_CSP = 2, MODE_DENSE_CS = 3, MODE_CS_ONLY = 4, MODE_DENSE_CS1 = 6
+};
 
 struct AttnParams {
   int B, H, Lq, Lkv, mode;
@@ -121,7 +127,10 @@ struct Smem {
   static constexpr int kList = kAux + kBarBytes;
   static constexpr int kNegC = kList + kSchedStages * 2 * kMaxSteps * 2;    // [slot][128] fp32: -(M_i + log2 L_i)
   static constexpr int kXchg = kNegC + 2 * 128 * 4;  // [item parity][m_ref, l, m_true][128] fp32: slot 1 -> slot 0 of a split tile
-  static constexpr int kTotal = kXchg + 2 * 3 * 128 * 4;
+  // MODE_DENSE_CS1: per-warp column sums of a tile [slot][buffer][warp][128] fp32, and the rows' sums [slot][128]
+  static constexpr int kPart = kXchg + 2 * 3 * 128 * 4;
+  static constexpr int kRowL = kPart + 2 * 2 * 4 * 128 * 4;
+  static constexpr int kTotal = kRowL + 2 * 128 * 4;
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -150,6 +159,8 @@ struct Bars {
   uint64_t sched_full[kSchedStages], sched_empty[kSchedStages];
   uint64_t mma_done;
   uint64_t xchg_full[2];  // split tile: slot 1's partial result is complete (128 arrivals), by item parity
+  uint64_t part_full[2][2];  // MODE_DENSE_CS1: the four warps' column sums of a tile are in shared memory [slot][buffer]
+  uint64_t rowl_full[2];     // MODE_DENSE_CS1: the rows' probability sums of an item are in shared memory [slot]
   // column-sum sweep (MODE_DENSE_CS): S^T of a slot is double-buffered, [slot][buffer]
   uint64_t cs_full[2][2], cs_empty[2][2];
   SchedEntry sched[kSchedStages];
@@ -180,6 +191,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint16_t* lists = reinterpret_cast<uint16_t*>(smem + SM::kList);  // [kSchedStages][kMaxSteps]
   float* negc = reinterpret_cast<float*>(smem + SM::kNegC);
   float* xchg = reinterpret_cast<float*>(smem + SM::kXchg);
+  float* part = reinterpret_cast<float*>(smem + SM::kPart);
+  float* rowl = reinterpret_cast<float*>(smem + SM::kRowL);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -212,6 +225,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(&bars->mma_done, 1);
     mbar_init(&bars->xchg_full[0], 128);
     mbar_init(&bars->xchg_full[1], 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->part_full[s][0], 128);
+      mbar_init(&bars->part_full[s][1], 128);
+      mbar_init(&bars->rowl_full[s], 128);
+    }
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -314,6 +332,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int n_o = 0;  // items in which this slot produced an output (parity of o_full)
     int n_cs[2] = {0, 0};  // column-sum sweep: S^T tiles read per buffer (parity of cs_full)
     int n_xc[2] = {0, 0};  // split tiles merged so far, by item parity (parity of xchg_full)
+    int n_part[2] = {0, 0};  // MODE_DENSE_CS1: tiles reduced per buffer (parity of part_full)
+    int n_rowl = 0;          // MODE_DENSE_CS1: items with tiles (parity of rowl_full)
     bool ok = true;
 
     for (int n = 0; ok; ++n) {
@@ -329,7 +349,136 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
       int it = 0;
-      const int n_first = stats_given ? 0 : n_mine;
+      if (MODE == MODE_DENSE_CS1 && n_mine > 0) {
+        // ---- one sweep with the caller's row statistics.  S is read in the 16x256b shape: a thread holds FOUR
+        // query rows (lanes tq, tq + 8, tq + 16, tq + 24 of the warp's window, tq = lane / 4) x 32 columns
+        // (8k + 2 tc, + 1; tc = lane % 4), so the column sums start as in-thread adds over the four rows and
+        // finish with a 28-shuffle transposing butterfly over the eight threads that share tc.  P goes back to
+        // TMEM in the matching 16x128b shape.  p = exp2(s * scale - (M_i + log2 L_i)) is already normalised:
+        // no running maximum, no rescale of O; the rows' sums of p are kept so that O and the statistics stay
+        // exact for constants that are only approximately this attention's own.
+        const int tq = lane >> 2, tc = lane & 3;
+        float ncst[4];  // constants of rows tq + 8 i
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = im.row0[s] + quad * 32 + tq + 8 * i;
+          float c = -INFINITY;
+          if (rr < im.row_end[s]) {
+            const int64_t si = (int64_t)im.bh * p.Lq + rr;
+            const float Lr = p.L_in[si];
+            if (Lr > 0.f) c = -(p.M_in[si] + log2f(Lr));
+          }
+          ncst[i] = c;
+        }
+        uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // packed partial sums of p over this thread's columns, per row
+        const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+        const int tile = im.row0[s] >> 7;
+        float* cs_row = p.cs + im.b * p.cs_sb + im.h * p.cs_sh + (int64_t)(p.cs_pair ? tile >> 1 : tile) * p.cs_st;
+        const uint32_t b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+        const int col0 = 8 * ((b4 ? 8 : 0) + (b3 ? 4 : 0) + (b2 ? 2 : 0)) + 2 * tc;  // this thread's first result column
+        for (int j = 0; j < n_mine; ++j) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, wc, DEV_TIMEOUT_SOFTMAX));
+          if (!ok) break;
+          ++n_s;
+          tc_fence_after();
+          uint32_t ra[64], rb[64];
+          tmem_ld_16x256b_x16(tS, ra);
+          tmem_ld_16x256b_x16(tS + (16u << 16), rb);
+          tmem_wait_ld();
+          const int valid = p.Lkv - j * 128;
+          uint64_t acc2[16];
+          auto half_tile = [&](const uint32_t (&r)[64], int h, auto masked_tag) {
+            constexpr bool MASKED = decltype(masked_tag)::value;
+            const uint64_t nA = pack_f32x2(ncst[2 * h], ncst[2 * h]), nB = pack_f32x2(ncst[2 * h + 1], ncst[2 * h + 1]);
+            uint32_t pk[32];
+#pragma unroll
+            for (int kk = 0; kk < 16; ++kk) {
+              const uint64_t X = ffma2(pack_f32x2(__uint_as_float(r[4 * kk]), __uint_as_float(r[4 * kk + 1])), sc2, nA);
+              const uint64_t Y = ffma2(pack_f32x2(__uint_as_float(r[4 * kk + 2]), __uint_as_float(r[4 * kk + 3])), sc2, nB);
+              float x0, x1, y0, y1;
+              unpack_f32x2(X, x0, x1);
+              unpack_f32x2(Y, y0, y1);
+              x0 = fast_exp2(x0); x1 = fast_exp2(x1); y0 = fast_exp2(y0); y1 = fast_exp2(y1);
+              if (MASKED) {  // columns past the end of K
+                const int c = 8 * kk + 2 * tc;
+                if (c >= valid) x0 = y0 = 0.f;
+                if (c + 1 >= valid) x1 = y1 = 0.f;
+              }
+              const uint64_t PX = pack_f32x2(x0, x1), PY = pack_f32x2(y0, y1);
+              rs2[2 * h] = fadd2(rs2[2 * h], PX);
+              rs2[2 * h + 1] = fadd2(rs2[2 * h + 1], PY);
+              acc2[kk] = h == 0 ? fadd2(PX, PY) : fadd2(acc2[kk], fadd2(PX, PY));
+              pk[2 * kk] = pack_bf16x2(x0, x1);
+              pk[2 * kk + 1] = pack_bf16x2(y0, y1);
+            }
+            tmem_st_16x128b_x16(tS + ((uint32_t)(16 * h) << 16), pk);
+          };
+          if (valid < 128) {
+            half_tile(ra, 0, std::true_type{});
+            half_tile(rb, 1, std::true_type{});
+          } else {
+            half_tile(ra, 0, std::false_type{});
+            half_tile(rb, 1, std::false_type{});
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bars->p_full[s]);
+          // ---- column sums of the warp's 32 rows: transposing butterfly over lane bits 4, 3, 2 (fixed order)
+          float a[32];
+#pragma unroll
+          for (int kk = 0; kk < 16; ++kk) unpack_f32x2(acc2[kk], a[2 * kk], a[2 * kk + 1]);
+          float c16[16], d8[8], e4[4];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            c16[i] = (b4 ? a[i + 16] : a[i]) + __shfl_xor_sync(0xffffffffu, b4 ? a[i] : a[i + 16], 16);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            d8[i] = (b3 ? c16[i + 8] : c16[i]) + __shfl_xor_sync(0xffffffffu, b3 ? c16[i] : c16[i + 8], 8);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            e4[i] = (b2 ? d8[i + 4] : d8[i]) + __shfl_xor_sync(0xffffffffu, b2 ? d8[i] : d8[i + 4], 4);
+          // e4[0..1]: columns col0, col0 + 1; e4[2..3]: columns col0 + 8, col0 + 9
+          const int buf = j & 1;
+          float* pw = part + ((s * 2 + buf) * 4 + quad) * 128;
+          *reinterpret_cast<float2*>(pw + col0) = make_float2(e4[0], e4[1]);
+          *reinterpret_cast<float2*>(pw + col0 + 8) = make_float2(e4[2], e4[3]);
+          mbar_arrive(&bars->part_full[s][buf]);
+          ok = __all_sync(0xffffffffu, mbar_wait(&bars->part_full[s][buf], n_part[buf] & 1, wc, DEV_TIMEOUT_SOFTMAX));
+          if (!ok) break;
+          ++n_part[buf];
+          const float* pr = part + (s * 2 + buf) * 4 * 128 + r_in_tile;
+          const float colsum = ((pr[0] + pr[128]) + pr[256]) + pr[384];
+          const int key = j * 128 + r_in_tile;
+          if (key < p.Lkv) {
+            if (p.cs_pair) atomicAdd(cs_row + key, colsum);  // two addends onto zero: the same bits in either order
+            else cs_row[key] = colsum;
+          }
+          ++it;
+        }
+        if (!ok) break;
+        // the rows' sums of p: over this thread's columns, then over the four threads that share the rows
+        float rs[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float x0, x1;
+          unpack_f32x2(rs2[i], x0, x1);
+          float v = x0 + x1;
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          rs[i] = v;
+        }
+        if (tc == 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) rowl[s * 128 + quad * 32 + tq + 8 * i] = rs[i];
+        }
+        mbar_arrive(&bars->rowl_full[s]);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->rowl_full[s], n_rowl & 1, wc, DEV_TIMEOUT_SOFTMAX));
+        if (!ok) break;
+        ++n_rowl;
+        l = rowl[s * 128 + r_in_tile];  // this thread's own row from here on (epilogue: thread = row)
+        m_ref = m_true = 0.f;
+      }
+      const int n_first = (stats_given || MODE == MODE_DENSE_CS1) ? 0 : n_mine;
       for (int j = 0; j < n_first; ++j) {
         const int kvb = (MODE == MODE_BLOCK) ? (mylist[j] & 0xFFF) : j + (s == 1 ? e.off1 : 0);
         const uint32_t sub = (MODE == MODE_BLOCK) ? ((uint32_t)mylist[j] >> 12 >> (2 * (r_in_tile >> 6))) & 3u : 3u;
@@ -553,6 +702,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int64_t si = (int64_t)im.bh * p.Lq + row;
         m_ref = row_ok ? p.M_in[si] : -INFINITY;
         l = row_ok ? p.L_in[si] : 0.f;
+      } else if (MODE == MODE_DENSE_CS1) {
+        // statistics out: the given pair with L corrected by the measured row sum, so that 2^M * L is this
+        // attention's true normaliser even when the given constants were another pass's
+        if (row_ok && p.L) {
+          const int64_t si = (int64_t)im.bh * p.Lq + row;
+          if (p.M) p.M[si] = p.M_in[si];
+          p.L[si] = p.L_in[si] * l;
+        }
       } else if (row_ok && MODE != MODE_CSP && !(split && s == 1)) {
         const int64_t si = (int64_t)im.bh * p.Lq + row;
         if (p.M) p.M[si] = m_stat;
@@ -1124,6 +1281,7 @@ int launch_d(int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     case MODE_BLOCK: return launch_mode<D, MODE_BLOCK>(tq, tk, tv, p, grid, stream);
     case MODE_DENSE_CS: return launch_mode<D, MODE_DENSE_CS>(tq, tk, tv, p, grid, stream);
     case MODE_CS_ONLY: return launch_mode<D, MODE_CS_ONLY>(tq, tk, tv, p, grid, stream);
+    case MODE_DENSE_CS1: return launch_mode<D, MODE_DENSE_CS1>(tq, tk, tv, p, grid, stream);
     default: return launch_mode<D, MODE_CSP>(tq, tk, tv, p, grid, stream);
   }
 }
@@ -1131,7 +1289,7 @@ int launch_d(int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUten
 }  // namespace
 
 // mode: an AttnMode, or MODE_CS_ONLY + 1 for the column sums from row statistics the caller supplies in
-// a->M / a->L.
+// a->M / a->L.  MODE_DENSE_CS1 reads its row statistics from a->M_in / a->L_in.
 int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
   LVAR_REQUIRE(a != nullptr, LVAR_ERR_ARG, "null argument block");
   const bool stats_given = mode == MODE_CS_ONLY + 1;
@@ -1171,7 +1329,14 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     p.L_in = a->L;
     p.M = p.L = nullptr;
   }
-  if (mode == MODE_DENSE_CS || mode == MODE_CS_ONLY) {
+  if (mode == MODE_DENSE_CS1) {
+    LVAR_REQUIRE(a->M_in && a->L_in, LVAR_ERR_ARG,
+                 "M_in and L_in (row statistics of this attention, fp32 [B,H,Lq]) must be non-null");
+    LVAR_REQUIRE((a->M == nullptr) == (a->L == nullptr), LVAR_ERR_ARG, "M and L (statistics out) go together");
+    p.M_in = a->M_in;
+    p.L_in = a->L_in;
+  }
+  if (mode == MODE_DENSE_CS || mode == MODE_CS_ONLY || mode == MODE_DENSE_CS1) {
     LVAR_REQUIRE(a->cs != nullptr, LVAR_ERR_ARG, "cs (column sums per 128-row query tile) is null");
     p.cs = a->cs;
     p.cs_sb = a->cs_sb;
@@ -1203,7 +1368,7 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     p.m_sh = a->bm_sh;
     p.m_sq = a->bm_sq;
   }
-  if (mode == MODE_DENSE || mode == MODE_DENSE_CS || mode == MODE_CS_ONLY) {
+  if (mode == MODE_DENSE || mode == MODE_DENSE_CS || mode == MODE_CS_ONLY || mode == MODE_DENSE_CS1) {
     LVAR_REQUIRE(p.nkb <= 16383, LVAR_ERR_UNSUPPORTED, "Lkv too long (max %d keys)", 16383 * 128);
   }
   if (mode == MODE_CSP) {

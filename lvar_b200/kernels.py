@@ -129,6 +129,39 @@ def dense_colsum_attn_fwd(q, k, v, scale=None, *, return_stats=False, status=Non
     return (o, cs, M, L) if return_stats else (o, cs)
 
 
+def dense_colsum_attn_given_fwd(q, k, v, M, L, scale=None, *, return_stats=False, status=None, group_tiles=1):
+    """Dense attention and its column sums in ONE sweep from given row statistics (M, L as ``dense_attn_fwd``
+    returns them): (o, cs) with cs fp32 [B,H,ceil(Lq/(128*group_tiles)),Lkv] normalised by the given statistics;
+    with ``return_stats`` also this attention's own statistics (M, L times the measured row sums)."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(n, t)
+    if group_tiles not in (1, 2):
+        raise RuntimeError("group_tiles must be 1 or 2")
+    B, H, Lq, _ = q.shape
+    Lkv = k.shape[2]
+    for n, t in (("M", M), ("L", L)):
+        if t.dtype != torch.float32 or not t.is_cuda or t.numel() != B * H * Lq or not t.is_contiguous():
+            raise RuntimeError(f"{n} must be a contiguous CUDA float32 tensor with B*H*Lq elements")
+    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    rows = 128 * group_tiles
+    cs = (torch.zeros if group_tiles == 2 else torch.empty)((B, H, (Lq + rows - 1) // rows, Lkv),
+                                                            dtype=torch.float32, device=q.device)
+    a = AttnArgs()
+    stream = _fill_qkv(a, q, k, v, o, scale)
+    a.cs, a.cs_sb, a.cs_sh, a.cs_st = cs.data_ptr(), cs.stride(0), cs.stride(1), cs.stride(2)
+    a.cs_group_tiles = group_tiles
+    a.M_in, a.L_in = M.data_ptr(), L.data_ptr()
+    Mo = Lo = None
+    if return_stats:
+        Mo = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        Lo = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        a.M, a.L = Mo.data_ptr(), Lo.data_ptr()
+    if status is not None:
+        a.dev_status = status.data_ptr()
+    check(lib.lvar_dense_colsum_attn_given(C.byref(a), stream))
+    return (o, cs, Mo, Lo) if return_stats else (o, cs)
+
+
 def colsum_tiles_fwd(q, k, scale=None, *, stats=None, return_stats=False, status=None):
     """Attention column sums of every 128-row query tile without the attention output: fp32
     [B,H,ceil(Lq/128),Lkv].  ``stats`` = (M, L) as ``dense_attn_fwd`` returns them skips the statistics sweep;

@@ -43,11 +43,23 @@ def _dense_attn_scaled(q, k, v, scale: float):
 
 
 def _dense_colsum_attn_scaled(q, k, v, p, scale: float):
-    o, M, L = K.dense_attn_fwd(q, k, v, scale)
     B, H, Lq, _ = q.shape
-    # p = 1/sum exp(s): in the kernel's base-2 form that is M' = -log2(p), L' = 1
-    Mp = (-torch.log2(p.reshape(B, H, Lq).float())).contiguous()
-    cs = K.colsum_groups_fwd(q, k, Mp, torch.ones_like(Mp), get_kernel_config_attn()["bm"], scale)
+    # p = 1/sum exp(s): in the kernels' base-2 form that is M' = -log2(p), L' = 1.  A p that underflowed to 0
+    # (row maximum above 127 in base 2) is clamped to the smallest normal number instead of giving inf / NaN.
+    Mp = (-torch.log2(p.reshape(B, H, Lq).float().clamp_min(torch.finfo(torch.float32).tiny))).contiguous()
+    ones = torch.ones_like(Mp)
+    bm = get_kernel_config_attn()["bm"]
+    if bm % 128 == 0:
+        # one sweep: the probabilities that feed P V are normalised with p as they are formed and their column
+        # sums come from the same registers (the reference kernel's form, dense_colsum_attn.cu:270-280)
+        if bm == 256:
+            o, cs, M, L = K.dense_colsum_attn_given_fwd(q, k, v, Mp, ones, scale, return_stats=True, group_tiles=2)
+        else:
+            o, cs128, M, L = K.dense_colsum_attn_given_fwd(q, k, v, Mp, ones, scale, return_stats=True)
+            cs = K.sum_tiles(cs128, bm // 128)
+    else:
+        o, M, L = K.dense_attn_fwd(q, k, v, scale)
+        cs = K.colsum_fwd(q, k, Mp, ones, bm, scale)
     return [o, cs, _l_vec(M, L)]
 
 

@@ -100,7 +100,7 @@ def test_2048px_style_last_scale_window_plus_topk(K):
     ones = torch.ones(nq, nk, dtype=torch.bool, device="cuda")
     d1, _, _ = K.dense_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], scale)
     assert torch.equal(K.block_sparse_attn_fwd(q[:1, :1], k[:1, :1], v[:1, :1], ones, scale), d1)
-    assert (d1.float() - o_d[:1, :1].float()).abs().max().item() <= 1.6e-2
+    assert (d1.float() - o_d[:1, :1].float()).abs().max().item() <= 3.2e-2  # one bf16 ulp below 8
 
 
 @pytest.mark.parametrize("variant", ["softmax_scale_1_over_sqrt_d", "cosine_attention_scale_1"])

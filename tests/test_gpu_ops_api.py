@@ -38,7 +38,7 @@ def test_dense_attn_and_colsum_return_conventions(ops):
         _, cs_ref = oa.dense_colsum_attn(q, k, v, 0.1, q_group_size=bm, dtype=torch.float64)
         assert ((cs.double().cpu() - cs_ref).abs() / cs_ref).max() <= 1e-3
         # same attention, but the two launches may schedule their last tiles differently: equal to rounding
-        assert (o2.float() - o.float()).abs().max() <= 1.6e-2
+        assert (o2.float() - o.float()).abs().max() <= 3.2e-2  # one bf16 ulp below 8
         assert (o2.float().cpu() - o_ref).abs().max() <= 2e-2
     # the materialising helper agrees with the kernels
     o3, cs3 = ops.naive_dense_colsum_attn(qc.float(), kc.float(), vc.float(), 0.1, q_group_size=bm)
@@ -110,7 +110,9 @@ def test_torch_ops_chipmunk_namespace(ops):
     o2, cs, l2 = torch.ops.chipmunk.dense_colsum_attn(qc, kc, vc, l_vec)
     _, cs_ref = oa.dense_colsum_attn(q, k, v, 1.0, q_group_size=256, dtype=torch.float64)
     assert ((cs.double().cpu() - cs_ref).abs() / cs_ref).max() <= 1e-3
-    assert torch.equal(o2, o) and torch.equal(l2, l_vec)
+    # the output and the normaliser come from the one-sweep kernel here: equal to the dense kernel's to rounding
+    assert (o2.float() - o.float()).abs().max() <= 3.2e-2 and (o2.float().cpu() - o_ref).abs().max() <= 2e-2
+    assert torch.allclose(l2, l_vec, rtol=2e-3)
     # csp_attn accumulates in place
     inds = torch.arange(520, dtype=torch.int32).expand(1, 2, 2, 520).contiguous().cuda()
     counts = torch.full((1, 2, 2), 520, dtype=torch.int32, device="cuda")
