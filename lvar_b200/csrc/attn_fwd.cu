@@ -161,7 +161,6 @@ struct Bars {
   uint64_t xchg_full[2];  // split tile: slot 1's partial result is complete (128 arrivals), by item parity
   uint64_t part_full[2][2];  // MODE_DENSE_CS1: the four warps' column sums of a tile are in shared memory [slot][buffer]
   uint64_t rowl_full[2];     // MODE_DENSE_CS1: the rows' probability sums of an item are in shared memory [slot]
-  uint64_t stage_full[2];    // the slot's output tile is staged in shared memory (128 arrivals) [slot]
   // column-sum sweep (MODE_DENSE_CS): S^T of a slot is double-buffered, [slot][buffer]
   uint64_t cs_full[2][2], cs_empty[2][2];
   SchedEntry sched[kSchedStages];
@@ -183,11 +182,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t IDESC_PV = make_idesc_bf16(128, D, 0, 1);
   constexpr uint32_t TM_O = 256;
   constexpr bool kHasCs = MODE == MODE_DENSE_CS || MODE == MODE_CS_ONLY;  // column-sum sweep after the first one
-  // The output tile of a slot goes through shared memory - the slot's Q tile, dead after the item's last Q K^T -
-  // so that it leaves the SM as whole rows: a thread owns a query ROW of the accumulator, and 32 rows per store
-  // instruction are 32 separate cache lines (measured: about 5 us per work item).  The column-sum sweep reads Q
-  // again after the epilogue, so those modes keep the direct stores.
-  constexpr bool kStageOut = !kHasCs;
   // MODE_CS_ONLY with the caller's row statistics: no first sweep at all
   const bool stats_given = MODE == MODE_CS_ONLY && p.M_in != nullptr;
 
@@ -207,11 +201,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // ---------------------------------------------------------------- setup
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
-    // the Q tiles are free again when the item's last MMA has completed and, where the output is staged in
-    // them, when every softmax thread has read its part of the staged tile back
-    mbar_init(&bars->q_empty, kStageOut ? 1 + 256 : 1);
-    mbar_init(&bars->stage_full[0], 128);
-    mbar_init(&bars->stage_full[1], 128);
+    mbar_init(&bars->q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars->k_full[i], MODE == MODE_CSP ? 32 : 1);
       mbar_init(&bars->k_empty[i], 1);
@@ -344,7 +334,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int n_xc[2] = {0, 0};  // split tiles merged so far, by item parity (parity of xchg_full)
     int n_part[2] = {0, 0};  // MODE_DENSE_CS1: tiles reduced per buffer (parity of part_full)
     int n_rowl = 0;          // MODE_DENSE_CS1: items with tiles (parity of rowl_full)
-    int n_stage = 0;         // items whose output this warpgroup staged (parity of stage_full)
     bool ok = true;
 
     for (int n = 0; ok; ++n) {
@@ -612,7 +601,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           x[256 + r_in_tile] = m_true;
           tc_fence_before();
           mbar_arrive(&bars->xchg_full[n & 1]);
-          if (kStageOut && max(e.n0, e.n1) > 0) mbar_arrive(&bars->q_empty);
         } else {
           float w0 = (it > 0 && l > 0.f) ? (1.0f / l) : 0.f, w1 = 0.f;  // out = O_0 * w0 + O_1 * w1
           bool other = false;  // slot 1 holds a partial result of this tile
@@ -636,32 +624,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             l_stat = lt > 0.f ? lt * fast_exp2(mm - m_stat) : 0.f;
           }
           const uint32_t tO1 = tmem_base + lane_off + TM_O + (uint32_t)D;  // slot 1's accumulator (split tiles)
-          __nv_bfloat16* obase = p.o + im.b * p.o_sb + im.h * p.o_sh;
-          __nv_bfloat16* orow = obase + (int64_t)row * p.o_sl;
-          const __nv_bfloat16* ibase = (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh) : nullptr;
-          const __nv_bfloat16* irow = (MODE == MODE_CSP) ? (ibase + (int64_t)row * p.oi_sl) : nullptr;
+          __nv_bfloat16* orow = p.o + im.b * p.o_sb + im.h * p.o_sh + (int64_t)row * p.o_sl;
+          const __nv_bfloat16* irow =
+              (MODE == MODE_CSP) ? (p.o_in + im.b * p.oi_sb + im.h * p.oi_sh + (int64_t)row * p.oi_sl) : nullptr;
           // accumulate input taken from a coarser token grid: this row's four source tokens and weights
           const bool resize = (MODE == MODE_CSP) && p.oi_side > 0;
           BilinearTaps tp = {};
-          if (resize && row_ok) tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
-          // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
-          // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
-          auto accumulate = [&](uint4 delta, uint4 prev) {
-            const uint32_t dv[4] = {delta.x, delta.y, delta.z, delta.w}, pv[4] = {prev.x, prev.y, prev.z, prev.w};
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float d0 = __uint_as_float(dv[i] << 16), d1 = __uint_as_float(dv[i] & 0xffff0000u);
-              const float a0 = __uint_as_float(pv[i] << 16), a1 = __uint_as_float(pv[i] & 0xffff0000u);
-              w[i] = pack_bf16x2(fmaf(p.o_scale, d0, a0), fmaf(p.o_scale, d1, a1));
-            }
-            return make_uint4(w[0], w[1], w[2], w[3]);
-          };
-          uint8_t* stg = sQ + s * SM::kTile;  // staging area: this slot's Q tile, same swizzled [128][64] sub-tiles
-          // Staged only when the slot ran tiles in this item: its four warps then went through the tiles' barriers
-          // together, so none of them can still be reading the previous item's staged tile.  A slot without tiles
-          // writes its zeros directly.
-          const bool staged = kStageOut && it > 0;
+          const __nv_bfloat16* ibase = nullptr;
+          if (resize && row_ok) {
+            tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
+            ibase = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
+          }
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t r[32];
@@ -690,18 +663,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               if (it > 0) mbar_arrive(&bars->o_empty[s]);
               if (split && other) mbar_arrive(&bars->o_empty[1]);
             }
+            if (row_ok) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint32_t w[4];
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint32_t w[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                w[i] = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2 * i]), __uint_as_float(r[q4 * 8 + 2 * i + 1]));
-              uint4 val = make_uint4(w[0], w[1], w[2], w[3]);
-              if (staged) {
-                const int cc = c * 4 + q4;  // 16-byte chunk of the row
-                *reinterpret_cast<uint4*>(stg + (cc >> 3) * 16384 + r_in_tile * 128 + (((cc & 7) ^ (r_in_tile & 7)) << 4)) = val;
-              } else if (row_ok) {
+                for (int i = 0; i < 4; ++i)
+                  w[i] = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2 * i]), __uint_as_float(r[q4 * 8 + 2 * i + 1]));
                 if (MODE == MODE_CSP) {
+                  // out = bf16(o_in + o_scale * bf16(delta)): same rounding points as the reference's
+                  // `o + o_delta * o_scale` on bf16 tensors (kernels/sparse_attn/sparse_attn_ops.py:288).
                   uint4 prev;
                   if (resize) {
                     const __nv_bfloat16* ib = ibase + c * 32 + q4 * 8;
@@ -712,56 +683,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                   } else {
                     prev = *reinterpret_cast<const uint4*>(irow + c * 32 + q4 * 8);
                   }
-                  val = accumulate(val, prev);
-                }
-                *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = val;
-              }
-            }
-          }
-          if (staged) {
-            BilinearTaps* taps = reinterpret_cast<BilinearTaps*>(part) + s * 128;  // (the column-sum area is free here)
-            if (resize) taps[r_in_tile] = tp;
-            mbar_arrive(&bars->stage_full[s]);
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars->stage_full[s], n_stage & 1, wc, DEV_TIMEOUT_SOFTMAX));
-            if (!ok) break;
-            ++n_stage;
-            // read the tile back row-major: a warp covers whole rows (32 consecutive 16-byte chunks)
-            constexpr int CH = D / 8;
-            uint4 vals[CH];
+                  const uint32_t pv[4] = {prev.x, prev.y, prev.z, prev.w};
 #pragma unroll
-            for (int i = 0; i < CH; ++i) {
-              const int u = i * 128 + r_in_tile, rr = u / CH, cc = u % CH;
-              vals[i] = *reinterpret_cast<const uint4*>(stg + (cc >> 3) * 16384 + rr * 128 + (((cc & 7) ^ (rr & 7)) << 4));
-            }
-            // the staged tile is in registers: the loader may bring the next item's Q tiles in (they arrive through
-            // the async proxy, the staging went through the generic one: order the two)
-            fence_proxy_async_smem();
-            mbar_arrive(&bars->q_empty);
-#pragma unroll
-            for (int i = 0; i < CH; ++i) {
-              const int u = i * 128 + r_in_tile, rr = u / CH, cc = u % CH;
-              const int grow = im.row0[s] + rr;
-              if (grow < im.row_end[s]) {
-                uint4 val = vals[i];
-                if (MODE == MODE_CSP) {
-                  uint4 prev;
-                  if (resize) {
-                    const BilinearTaps t = taps[rr];
-                    const __nv_bfloat16* ib = ibase + cc * 8;
-                    prev = bilinear_mix8(t, *reinterpret_cast<const uint4*>(ib + (int64_t)t.r00 * p.oi_sl),
-                                         *reinterpret_cast<const uint4*>(ib + (int64_t)t.r01 * p.oi_sl),
-                                         *reinterpret_cast<const uint4*>(ib + (int64_t)t.r10 * p.oi_sl),
-                                         *reinterpret_cast<const uint4*>(ib + (int64_t)t.r11 * p.oi_sl));
-                  } else {
-                    prev = *reinterpret_cast<const uint4*>(ibase + (int64_t)grow * p.oi_sl + cc * 8);
+                  for (int i = 0; i < 4; ++i) {
+                    const float d0 = __uint_as_float(w[i] << 16), d1 = __uint_as_float(w[i] & 0xffff0000u);
+                    const float a0 = __uint_as_float(pv[i] << 16), a1 = __uint_as_float(pv[i] & 0xffff0000u);
+                    w[i] = pack_bf16x2(fmaf(p.o_scale, d0, a0), fmaf(p.o_scale, d1, a1));
                   }
-                  val = accumulate(val, prev);
                 }
-                *reinterpret_cast<uint4*>(obase + (int64_t)grow * p.o_sl + cc * 8) = val;
+                *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
               }
             }
-          } else if (kStageOut && max(e.n0, e.n1) > 0) {
-            mbar_arrive(&bars->q_empty);  // nothing staged, but the other slot ran tiles: the barrier counts every thread
           }
         }
       }

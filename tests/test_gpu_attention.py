@@ -50,12 +50,11 @@ SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT = 1, 2  # lvar_attn_args.sched_flags
 
 
 def _same_to_rounding(a, b):
-    """Two bf16 results of the same attention whose probabilities were rounded to bf16 against different reference
-    maxima and summed in a different order: they differ by the bf16 rounding of P (2^-9 relative per term, a few
-    1e-3 absolute on outputs of order one) plus one bf16 ulp of the result, and agree far better on average."""
+    """Two bf16 results of the same attention formed in a different fp32 summation order: equal up to one bf16
+    ulp (2^-7 relative; the outputs stay below 8 in magnitude) and almost everywhere bit-equal."""
     a, b = a.float(), b.float()
     d = (a - b).abs()
-    assert (d <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 4e-3).all(), f"max-abs {d.max().item():.3e}"
+    assert (d <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-6).all(), f"max-abs {d.max().item():.3e}"
     assert d.mean().item() <= 5e-4, f"mean-abs {d.mean().item():.3e}"
 
 
