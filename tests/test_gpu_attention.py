@@ -50,12 +50,14 @@ SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT = 1, 2  # lvar_attn_args.sched_flags
 
 
 def _same_to_rounding(a, b):
-    """Two bf16 results of the same attention formed in a different fp32 summation order: equal up to one bf16
-    ulp (2^-7 relative; the outputs stay below 8 in magnitude) and almost everywhere bit-equal."""
+    """Two bf16 results of the same attention whose probabilities were rounded to bf16 against different reference
+    maxima and summed in a different order.  A row that looks at one key carries that probability's bf16 rounding
+    (2^-9 relative) straight into the output, on top of the output's own rounding: up to two bf16 ulps (2^-6
+    relative) where the output is large, a few 1e-3 absolute where it is small; far less on average."""
     a, b = a.float(), b.float()
     d = (a - b).abs()
-    assert (d <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-6).all(), f"max-abs {d.max().item():.3e}"
-    assert d.mean().item() <= 5e-4, f"mean-abs {d.mean().item():.3e}"
+    assert (d <= 2.0 ** -6 * torch.maximum(a.abs(), b.abs()) + 4e-3).all(), f"max-abs {d.max().item():.3e}"
+    assert d.mean().item() <= 1.5e-3, f"mean-abs {d.mean().item():.3e}"
 
 
 def _ok_status(K, st):
