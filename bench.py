@@ -292,6 +292,8 @@ def leg_hbm_kernels(K, P, q, k, v, cs, scale, dev, hbm_gbs):
     rec("build_block_mask", scores.numel() * 5 + always.numel(), lambda: K.build_block_mask(scores, always, K_TOTAL))
     rec("mask_from_colsums(block_scores+build_block_mask)", cs.numel() * 4 + scores.numel() * 9,
         lambda: K.build_block_mask(K.block_scores(cs, BLOCK), always, K_TOTAL))
+    rec("block_mask_from_colsums(one pass)", cs.numel() * 4 + scores.numel(),
+        lambda: K.block_mask_from_colsums(cs, always, K_TOTAL, BLOCK))
     # decision-step top-k: 16 groups of 256 rows per head, 2176 of 10521 keys, lists padded to Lkv columns
     cs256 = K.sum_tiles(cs, 2).contiguous()
     rows = cs256.numel() // LKV
@@ -524,7 +526,7 @@ def run_ours(args):
         fused_ms = timed(lambda: K.dense_colsum_attn_fwd(q, k, v, scale), 10)  # attention + column sums, one launch
         cs_only_ms = timed(lambda: K.colsum_tiles_fwd(q, k, scale), 10)
         cs_given_ms = timed(lambda: K.colsum_tiles_fwd(q, k, scale, stats=(M, L)), 10)
-        mask_ms = timed(lambda: K.build_block_mask(K.block_scores(cs, BLOCK), always, K_TOTAL), 10)
+        mask_ms = timed(lambda: K.block_mask_from_colsums(cs, always, K_TOTAL, BLOCK), 10)
         extra.update({
             "dense_attn_ms": dense_ms, "dense_attn_tflops": dense_flops / dense_ms / 1e9,
             "dense_attn_frac_of_bf16_peak": dense_flops / dense_ms / 1e9 / peaks["bf16"],

@@ -195,6 +195,14 @@ int lvar_build_block_mask(const float* scores, const uint8_t* always, uint8_t* m
                           int32_t* counts, int64_t BH, int32_t nq, int32_t nk, int32_t k_total,
                           lvar_stream_t stream);
 
+/* lvar_block_scores + lvar_build_block_mask in one pass over the column sums: cs fp32 [BH*nq, Lkv] (rows
+ * cs_row_stride elements apart) -> mask uint8 [BH, nq, nk], nk = ceil(Lkv / block), with the same selection rule
+ * and the same bits in the block scores (scores_out, optional fp32 [BH, nq, nk]; lists / counts optional as in
+ * lvar_build_block_mask).  The column sums are read once and no score tensor has to exist in between. */
+int lvar_block_mask_from_colsums(const float* cs, int64_t cs_row_stride, const uint8_t* always, uint8_t* mask,
+                                 float* scores_out, int32_t* lists, int32_t* counts, int64_t BH, int32_t nq,
+                                 int32_t Lkv, int32_t block, int32_t k_total, lvar_stream_t stream);
+
 /* Exact, deterministic top-k of each row of an fp32 matrix [rows, n] (row_stride elements apart).
  * out int32 [rows, out_cols] (out_stride apart): the first k entries are the selected column ids,
  * descending by value with equal values in ascending index order, or, if ascending_index != 0, the

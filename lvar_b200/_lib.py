@@ -73,6 +73,8 @@ _SIGNATURES = {
                                                                                     C.c_void_p, C.c_uint64, C.c_void_p]),
     "lvar_block_scores": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
     "lvar_build_block_mask": (C.c_int, [C.c_void_p] * 5 + [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "lvar_block_mask_from_colsums": (C.c_int, [C.c_void_p, C.c_int64] + [C.c_void_p] * 5 +
+                                     [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "lvar_topk_indices": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p,
                                     C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "lvar_mask_to_indices": (C.c_int, [C.c_void_p] * 3 + [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),

@@ -72,6 +72,9 @@ int launch_block_scores(const float* cs, float* out, int64_t rows, int Lkv, int 
                         cudaStream_t stream);
 int launch_build_block_mask(const float* scores, const uint8_t* always, uint8_t* mask, int32_t* lists,
                             int32_t* counts, int64_t BH, int nq, int nk, int k_total, cudaStream_t stream);
+int launch_block_mask_from_colsums(const float* cs, int64_t cs_row_stride, const uint8_t* always, uint8_t* mask,
+                                   float* scores_out, int32_t* lists, int32_t* counts, int64_t BH, int nq, int Lkv,
+                                   int block, int k_total, cudaStream_t stream);
 int launch_topk(const float* scores, int64_t rows, int n, int64_t row_stride, int k, int ascending_index,
                 int32_t* out, int64_t out_stride, int out_cols, int32_t* counts, int count_value,
                 cudaStream_t stream);
@@ -189,6 +192,13 @@ int lvar_build_block_mask(const float* scores, const uint8_t* always, uint8_t* m
                           lvar_stream_t stream) {
   return lvar::launch_build_block_mask(scores, always, mask, lists, counts, BH, nq, nk, k_total,
                                        static_cast<cudaStream_t>(stream));
+}
+
+int lvar_block_mask_from_colsums(const float* cs, int64_t cs_row_stride, const uint8_t* always, uint8_t* mask,
+                                 float* scores_out, int32_t* lists, int32_t* counts, int64_t BH, int32_t nq,
+                                 int32_t Lkv, int32_t block, int32_t k_total, lvar_stream_t stream) {
+  return lvar::launch_block_mask_from_colsums(cs, cs_row_stride, always, mask, scores_out, lists, counts, BH, nq, Lkv,
+                                              block, k_total, static_cast<cudaStream_t>(stream));
 }
 
 int lvar_topk_indices(const float* scores, int64_t rows, int32_t n, int64_t row_stride, int32_t k,

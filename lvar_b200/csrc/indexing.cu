@@ -108,12 +108,83 @@ __global__ void build_block_mask_kernel(const float* __restrict__ scores, const 
   }
 }
 
+// Column sums -> block mask in one pass: one CTA (256 threads) per (b, h, q-block row) reads its row of column
+// sums once, forms the per-KV-block scores with block_scores_kernel's summation order (one warp per block: the
+// same bits) and selects as build_block_mask_kernel does.  Scores, lists and counts are optional outputs.
+__global__ void __launch_bounds__(256)
+block_mask_from_colsums_kernel(const float* __restrict__ cs, int64_t cs_row_stride, const uint8_t* __restrict__ always,
+                               uint8_t* __restrict__ mask, float* __restrict__ scores_out, int32_t* __restrict__ lists,
+                               int32_t* __restrict__ counts, int nq, int nk, int Lkv, int block, int k_total) {
+  extern __shared__ uint32_t sh[];
+  uint32_t* keys = sh;                                      // [nk]
+  uint8_t* flag = reinterpret_cast<uint8_t*>(keys + nk);    // [nk]
+  __shared__ int n_always;
+  const int64_t row = blockIdx.x;
+  const int qi = (int)(row % nq);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  if (threadIdx.x == 0) n_always = 0;
+  const float* src_row = cs + row * cs_row_stride;
+  for (int kb = warp; kb < nk; kb += n_warps) {
+    const float* src = src_row + (int64_t)kb * block;
+    const int valid = min(block, Lkv - kb * block);
+    float acc = 0.f;
+    for (int c = lane; c < block; c += 32) acc += (c < valid) ? src[c] : 0.f;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (lane == 0) {
+      keys[kb] = ordered_key(acc);
+      if (scores_out) scores_out[row * nk + kb] = acc;
+    }
+  }
+  __syncthreads();
+  int local = 0;
+  for (int j = threadIdx.x; j < nk; j += blockDim.x) {
+    const uint8_t a = always ? (always[(int64_t)qi * nk + j] != 0) : 0;
+    flag[j] = a;
+    local += a;
+  }
+  if (local) atomicAdd(&n_always, local);
+  __syncthreads();
+  const int need = max(0, k_total - n_always);
+  uint8_t* mrow = mask + row * nk;
+  for (int j = threadIdx.x; j < nk; j += blockDim.x) {
+    uint8_t sel = flag[j];
+    if (!sel && need > 0) {
+      const uint32_t kj = keys[j];
+      int rank = 0;
+      for (int i = 0; i < nk; ++i) {
+        if (flag[i]) continue;
+        const uint32_t ki = keys[i];
+        rank += (ki > kj) || (ki == kj && i < j);
+      }
+      sel = rank < need;
+    }
+    mrow[j] = sel;
+  }
+  if (lists != nullptr) {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int n = 0;
+      for (int base = 0; base < nk; base += 32) {
+        const int j = base + lane;
+        const bool on = (j < nk) && mrow[j];
+        const uint32_t vote = __ballot_sync(0xffffffffu, on);
+        if (on) lists[row * nk + n + __popc(vote & ((1u << lane) - 1u))] = j;
+        n += __popc(vote);
+      }
+      for (int j = n + lane; j < nk; j += 32) lists[row * nk + j] = -1;
+      if (lane == 0 && counts) counts[row] = n;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // exact top-k
 // ------------------------------------------------------------------------------------------------
 constexpr int kTopkThreads = 1024;
+constexpr int kHistCopies = 8, kHistStride = 257;
 
-// One CTA per row.  Shared: keys[n] | pairs[K2] (descending-value order only) | hist[256] | scan[64].
+// One CTA per row.  Shared: keys[n] | pairs[K2] (descending-value order only) | hist[8][257] | scan[64].
 __global__ void __launch_bounds__(kTopkThreads)
 topk_kernel(const float* __restrict__ scores, int64_t row_stride, int n, int k, int ascending_index,
             int32_t* __restrict__ out, int64_t out_stride, int out_cols, int32_t* __restrict__ counts,
@@ -121,7 +192,7 @@ topk_kernel(const float* __restrict__ scores, int64_t row_stride, int n, int k, 
   extern __shared__ __align__(16) uint8_t sh_raw[];
   uint32_t* keys = reinterpret_cast<uint32_t*>(sh_raw);
   unsigned long long* pairs = reinterpret_cast<unsigned long long*>(sh_raw + (((size_t)n * 4 + 15) & ~(size_t)15));
-  __shared__ int hist[256];
+  __shared__ int hist[kHistCopies * kHistStride];
   __shared__ int wsum_gt[32], wsum_eq[32];
   __shared__ uint32_t sh_prefix;
   __shared__ int sh_remaining;
@@ -141,26 +212,57 @@ topk_kernel(const float* __restrict__ scores, int64_t row_stride, int n, int k, 
   if (k > 0) {
     // radix select, most significant byte first: after 4 passes sh_prefix is the k-th largest key and
     // sh_remaining the number of elements equal to it that belong to the selection.
+    // Scores of one row share most of their leading bits (attention column sums span a few binades), so most
+    // keys of a pass fall into a handful of histogram bins: the histogram is kept in eight copies (one per lane
+    // modulo 8, 257 words apart so that equal bins of different copies sit in different banks), which cuts the
+    // serialisation of same-address atomics eightfold; the copies are added up when the bins are scanned.
     uint32_t maskbits = 0;
     for (int pass = 3; pass >= 0; --pass) {
-      for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
+      for (int i = tid; i < kHistCopies * kHistStride; i += kTopkThreads) hist[i] = 0;
       __syncthreads();
       const uint32_t prefix = sh_prefix;
       const int shift = pass * 8;
+      int* myhist = hist + (lane & (kHistCopies - 1)) * kHistStride;
       for (int i = tid; i < n; i += kTopkThreads) {
         const uint32_t key = keys[i];
-        if ((key & maskbits) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+        if ((key & maskbits) == prefix) atomicAdd(&myhist[(key >> shift) & 255u], 1);
       }
       __syncthreads();
-      if (tid == 0) {
-        int rem = sh_remaining;
-        int d = 255;
-        for (; d > 0; --d) {
-          if (hist[d] >= rem) break;
-          rem -= hist[d];
+      if (warp == 0) {
+        // bins from the top: the bin that holds the rem-th largest candidate.  Lane l owns bins 8l .. 8l+7.
+        const int rem = sh_remaining;
+        int binc[8];  // this lane's eight bins, summed over the copies
+        int own = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          int c = 0;
+#pragma unroll
+          for (int k2 = 0; k2 < kHistCopies; ++k2) c += hist[k2 * kHistStride + 8 * lane + j];
+          binc[j] = c;
+          own += c;
         }
-        sh_prefix = prefix | ((uint32_t)d << shift);
-        sh_remaining = rem;
+        int suffix = own;  // candidates in this lane's bins and all higher ones
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int t = __shfl_down_sync(0xffffffffu, suffix, d);
+          if (lane + d < 32) suffix += t;
+        }
+        const uint32_t reach = __ballot_sync(0xffffffffu, suffix >= rem);  // never empty: all candidates >= rem
+        const int L = 31 - __clz(reach);
+        if (lane == L) {
+          int r = rem - (suffix - own);  // still to find inside this lane's bins
+          int j = 7;
+#pragma unroll
+          for (int t = 7; t > 0; --t) {
+            if (j == t && binc[t] < r) {
+              r -= binc[t];
+              j = t - 1;
+            }
+          }
+          const int d = 8 * lane + j;
+          sh_prefix = prefix | ((uint32_t)d << shift);
+          sh_remaining = r;
+        }
       }
       maskbits |= 0xFFu << shift;
       __syncthreads();
@@ -371,6 +473,21 @@ int launch_build_block_mask(const float* scores, const uint8_t* always, uint8_t*
   const size_t smem = (size_t)nk * 5;
   build_block_mask_kernel<<<(unsigned)(BH * nq), 128, smem, stream>>>(scores, always, mask, lists, counts, nq, nk,
                                                                       k_total);
+  LVAR_CUDA_OK(cudaGetLastError());
+  return LVAR_OK;
+}
+
+int launch_block_mask_from_colsums(const float* cs, int64_t cs_row_stride, const uint8_t* always, uint8_t* mask,
+                                   float* scores_out, int32_t* lists, int32_t* counts, int64_t BH, int nq, int Lkv,
+                                   int block, int k_total, cudaStream_t stream) {
+  LVAR_REQUIRE(cs && mask, LVAR_ERR_ARG, "cs and mask must be non-null");
+  LVAR_REQUIRE(BH >= 1 && nq >= 1 && Lkv >= 1 && block >= 1, LVAR_ERR_ARG, "BH, nq, Lkv, block must be >= 1");
+  const int nk = (Lkv + block - 1) / block;
+  LVAR_REQUIRE(nk <= 8192, LVAR_ERR_LIMIT, "at most 8192 KV blocks per row (got %d)", nk);
+  LVAR_REQUIRE(BH * nq < (1ll << 31), LVAR_ERR_LIMIT, "too many rows");
+  const size_t smem = (size_t)nk * 5;
+  block_mask_from_colsums_kernel<<<(unsigned)(BH * nq), 256, smem, stream>>>(cs, cs_row_stride, always, mask, scores_out,
+                                                                             lists, counts, nq, nk, Lkv, block, k_total);
   LVAR_CUDA_OK(cudaGetLastError());
   return LVAR_OK;
 }

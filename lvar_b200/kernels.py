@@ -408,6 +408,31 @@ def build_block_mask(scores: torch.Tensor, always: Optional[torch.Tensor], k_tot
     return (mask, lists, counts) if return_lists else mask
 
 
+def block_mask_from_colsums(cs: torch.Tensor, always: Optional[torch.Tensor], k_total: int, block: int = 128, *,
+                            return_scores=False):
+    """``build_block_mask(block_scores(cs, block), always, k_total)`` in one launch and one pass over the column
+    sums: cs fp32 [B,H,G,Lkv] -> bool mask [B,H,G,ceil(Lkv/block)] (and the fp32 block scores with
+    ``return_scores``; the same bits as ``block_scores`` gives)."""
+    _require(cs.is_cuda and cs.dtype == torch.float32 and cs.dim() == 4 and cs.stride(-1) == 1,
+             "cs must be a CUDA float32 [B,H,G,Lkv] tensor with a contiguous last dimension")
+    if not cs.is_contiguous():
+        cs = cs.contiguous()
+    B, H, G, Lkv = cs.shape
+    nk = (Lkv + block - 1) // block
+    a_ptr = None
+    if always is not None:
+        _require(always.is_cuda and tuple(always.shape) == (G, nk), f"always must be a CUDA [{G},{nk}] tensor")
+        always = always.to(torch.uint8).contiguous() if always.dtype != torch.uint8 else always.contiguous()
+        a_ptr = always.data_ptr()
+    mask = torch.empty((B, H, G, nk), dtype=torch.uint8, device=cs.device)
+    scores = torch.empty((B, H, G, nk), dtype=torch.float32, device=cs.device) if return_scores else None
+    check(lib.lvar_block_mask_from_colsums(cs.data_ptr(), cs.stride(2), a_ptr, mask.data_ptr(),
+                                           scores.data_ptr() if scores is not None else None, None, None,
+                                           B * H, G, Lkv, int(block), int(k_total), _stream_ptr(cs.device)))
+    mask = mask.view(torch.bool)
+    return (mask, scores) if return_scores else mask
+
+
 def topk_indices(scores: torch.Tensor, k: int, *, ascending_index=False, out_cols: Optional[int] = None,
                  with_counts=False):
     """Exact deterministic top-k along the last dim of a float32 tensor -> int32 [..., out_cols]

@@ -600,3 +600,34 @@ def test_one_sweep_colsum_with_statistics_of_another_pass(K):
     w = torch.softmax(s, dim=-1) / f.cpu().double().unsqueeze(-1)
     ref = torch.stack([w[:, :, i * 128:(i + 1) * 128].sum(2) for i in range(3)], 2)
     assert _cs_rel(cs, ref) <= CS_REL
+
+
+@pytest.mark.parametrize("bm,resize", [(192, 0), (256, 0), (192, 40), (256, 48)])
+def test_csp_attn_many_work_items_per_sm(K, bm, resize):
+    """Column-sparse attention with more work items than SMs (every CTA runs several items back to back), ragged
+    last groups, with and without the O-cache resize, against the oracle on sampled heads."""
+    from oracle import attention as oa
+    from oracle import indexing as oi
+    B, H, Lq, Lkv, D = 2, 6, 4096, 3000, 128
+    q, k, v = _qkv(B, H, Lq, Lkv, D, seed=bm + resize, peaked=True)
+    G = (Lq + bm - 1) // bm
+    assert B * H * G > 148
+    g = torch.Generator().manual_seed(bm)
+    cap = 512
+    idx = torch.randint(0, Lkv, (B, H, G, Lkv), generator=g, dtype=torch.int32)
+    counts = torch.randint(1, cap + 1, (B, H, G), generator=g, dtype=torch.int32)
+    counts[0, 0, 3] = 0
+    src = resize * resize if resize else Lq
+    o_in = torch.randn(B, H, src, D, generator=g).bfloat16()
+    st = K.new_status("cuda")
+    o = K.csp_attn_fwd(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), counts.cuda(), o_in.cuda(), 1, bm, status=st,
+                       resize_from=resize)
+    _ok_status(K, st)
+    for b, h in ((0, 0), (1, 5), (0, 3)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        base = o_in[sl] if not resize else oi.upsample_ocache(o_in[sl].float(), src, Lq).bfloat16()
+        ref = oa.csp_attn(q[sl], k[sl], v[sl], None, idx[sl], counts[sl], base, 1, bm=bm)
+        d = (o[sl].float().cpu() - ref.float()).abs()
+        assert d.max().item() <= 3.2e-2 and d.mean().item() <= O_MEAN, (b, h, d.max().item())
+    assert torch.equal(o, K.csp_attn_fwd(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), counts.cuda(), o_in.cuda(), 1, bm,
+                                         resize_from=resize)), "bit-reproducible"

@@ -152,3 +152,29 @@ def test_sparse_step_lists_match_oracle(K, src_cols, s_count):
                                           count_value=s_count + band_count)
     assert torch.equal(got.cpu(), want)
     assert torch.equal(got_counts.cpu(), want_counts)
+
+
+@pytest.mark.parametrize("B,H,G,Lkv,block,k_total,peaked", [(2, 16, 32, 10521, 128, 17, True), (1, 2, 4, 680, 64, 6, False),
+                                                             (1, 3, 5, 1000, 128, 3, True), (2, 1, 1, 77, 128, 1, False)])
+def test_block_mask_from_colsums_equals_two_kernels(K, B, H, G, Lkv, block, k_total, peaked):
+    """One pass over the column sums gives the block scores of block_scores bit for bit and the mask of
+    build_block_mask; both are the oracle's on the same inputs (ragged last block, ties from a few distinct
+    values)."""
+    from oracle import indexing as oi
+    g = torch.Generator().manual_seed(Lkv + G)
+    cs = torch.rand(B, H, G, Lkv, generator=g)
+    if peaked:
+        cs = cs * torch.exp2(torch.randint(-20, 4, (B, H, G, Lkv), generator=g).float())
+    else:
+        cs = torch.round(cs * 4) / 4
+    nk = (Lkv + block - 1) // block
+    always = torch.rand(G, nk, generator=g) < 0.15
+    csc = cs.cuda()
+    scores = K.block_scores(csc, block)
+    want = K.build_block_mask(scores, always.cuda(), k_total)
+    mask, got_scores = K.block_mask_from_colsums(csc, always.cuda(), k_total, block, return_scores=True)
+    assert torch.equal(got_scores, scores) and torch.equal(mask, want)
+    assert torch.equal(K.block_mask_from_colsums(csc, always.cuda(), k_total, block), want)
+    assert torch.equal(mask.cpu(), oi.build_block_mask(scores.cpu(), always, k_total))
+    assert torch.equal(K.block_mask_from_colsums(csc, None, k_total, block),
+                       K.build_block_mask(scores, None, k_total))
