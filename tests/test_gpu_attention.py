@@ -51,12 +51,13 @@ SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT = 1, 2  # lvar_attn_args.sched_flags
 
 def _same_to_rounding(a, b):
     """Two bf16 results of the same attention whose probabilities were rounded to bf16 against different reference
-    maxima and summed in a different order.  A row that looks at one key carries that probability's bf16 rounding
-    (2^-9 relative) straight into the output, on top of the output's own rounding: up to two bf16 ulps (2^-6
-    relative) where the output is large, a few 1e-3 absolute where it is small; far less on average."""
+    maxima and summed in a different order.  Each probability carries a 2^-9 relative rounding error into the
+    output, weighted by |v| (up to about 4 here), whatever the size of the output itself, and the output is rounded
+    once more: the two results may differ by as much as each may differ from the exact one (the 2e-2 bar, plus one
+    bf16 ulp of outputs of magnitude 4 to 8), and agree far better on average."""
     a, b = a.float(), b.float()
     d = (a - b).abs()
-    assert (d <= 2.0 ** -6 * torch.maximum(a.abs(), b.abs()) + 4e-3).all(), f"max-abs {d.max().item():.3e}"
+    assert d.max().item() <= 3.2e-2, f"max-abs {d.max().item():.3e}"
     assert d.mean().item() <= 1.5e-3, f"mean-abs {d.mean().item():.3e}"
 
 
