@@ -62,6 +62,10 @@ def _sched_scratch(dev: int, stream: int, device: torch.device) -> int:
     device address.  The kernels leave the counter at zero, so it is allocated and cleared only once."""
     buf = _SCRATCH.get((dev, stream))
     if buf is None:
+        if torch.cuda.is_current_stream_capturing():
+            # allocated now, the counter and its zero fill would belong to the graph being captured
+            raise RuntimeError("first launch of an lvar_b200 attention kernel on this stream happens inside a CUDA "
+                               "graph capture: run one warm-up call on the capture stream before capturing")
         buf = torch.zeros(2, dtype=torch.int32, device=device)
         _SCRATCH[(dev, stream)] = buf
     return buf.data_ptr()
