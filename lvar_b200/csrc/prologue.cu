@@ -9,8 +9,11 @@
 // separate multiplies and add/subtract), one rounding to bf16 at the end: the reference keeps q and k in
 // fp32 and casts them to v's dtype at every call site.
 // rope(x)[2i] = cos[p,i] x[2i] - sin[p,i] x[2i+1],  rope(x)[2i+1] = sin[p,i] x[2i] + cos[p,i] x[2i+1],
-// p = rope_start + l.  One warp per (b, l, h); a lane holds c/32 consecutive elements (whole pairs).
+// p = rope_start + l.  One warp per (b, l, h) row, two rows per iteration; a lane holds c/32 consecutive elements
+// (whole pairs).
 #include <math.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -38,67 +41,83 @@ struct PrologueParams {
 template <int EPL>  // elements per lane: 2 (c = 64) or 4 (c = 128)
 __global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueParams p) {
   constexpr int C = EPL * 32;
+  constexpr int ROWS = 2;  // (b, l, h) rows per warp and iteration: their nine loads are issued before any arithmetic
+  using Vec = typename std::conditional<EPL == 4, uint2, uint32_t>::type;
   const int lane = threadIdx.x & 31;
   const int64_t rows = (int64_t)p.B * p.L * p.H;
-  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += (int64_t)gridDim.x * (blockDim.x >> 5)) {
-    const int h = (int)(row % p.H);
-    const int l = (int)((row / p.H) % p.L);
-    const int b = (int)(row / ((int64_t)p.H * p.L));
-    const __nv_bfloat16* src = p.qkv + b * p.s_b + l * p.s_l + h * p.s_h + lane * EPL;
-    const int pos = p.rope_start + l;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t row0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row0 < rows; row0 += warps * ROWS) {
+    Vec raw[ROWS][3];
+    int hh[ROWS], ll[ROWS], bb_[ROWS];
+    float cs[ROWS][EPL / 2], sn[ROWS][EPL / 2];
 #pragma unroll
-    for (int which = 0; which < 3; ++which) {
-      __nv_bfloat16 raw[EPL];
-      if (EPL == 4) {
-        *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src + which * p.s_w);
-      } else {
-        *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src + which * p.s_w);
-      }
-      __nv_bfloat16* dst;
-      if (which == 0) {
-        dst = p.q_out + b * p.q_sb + h * p.q_sh + (int64_t)l * p.q_sl;
-      } else if (which == 1) {
-        dst = p.k_cache + b * p.k_sb + h * p.k_sh + (int64_t)(p.cache_pos + l) * p.k_sl;
-      } else {
-        dst = p.v_cache + b * p.v_sb + h * p.v_sh + (int64_t)(p.cache_pos + l) * p.v_sl;
-      }
-      dst += lane * EPL;
-      if (which < 2) {
-        float x[EPL];
+    for (int r = 0; r < ROWS; ++r) {
+      const int64_t row = row0 + r * warps;
+      if (row >= rows) continue;
+      hh[r] = (int)(row % p.H);
+      ll[r] = (int)((row / p.H) % p.L);
+      bb_[r] = (int)(row / ((int64_t)p.H * p.L));
+      const __nv_bfloat16* src = p.qkv + bb_[r] * p.s_b + ll[r] * p.s_l + hh[r] * p.s_h + lane * EPL;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(raw[e]);
-        if (p.scale_mul != nullptr) {
-          float ssq = 0.f;
+      for (int which = 0; which < 3; ++which) raw[r][which] = *reinterpret_cast<const Vec*>(src + which * p.s_w);
+      if (p.cos_t != nullptr) {
+        const int64_t base = (int64_t)(p.rope_start + ll[r]) * (C / 2) + (lane * EPL >> 1);
 #pragma unroll
-          for (int e = 0; e < EPL; ++e) ssq = fmaf(x[e], x[e], ssq);
-#pragma unroll
-          for (int d = 16; d >= 1; d >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, d);
-          const float denom = fmaxf(sqrtf(ssq), 1e-12f);
-          const float mul = which == 0 ? p.scale_mul[h] : 1.0f;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) {
-            x[e] = __fdiv_rn(x[e], denom);
-            if (which == 0) x[e] = __fmul_rn(x[e], mul);
-          }
+        for (int e = 0; e < EPL / 2; ++e) {
+          cs[r][e] = p.cos_t[base + e];
+          sn[r][e] = p.sin_t[base + e];
         }
-        if (p.cos_t != nullptr) {
-#pragma unroll
-          for (int e = 0; e < EPL; e += 2) {
-            const int pair = (lane * EPL + e) >> 1;
-            const float cs = p.cos_t[(int64_t)pos * (C / 2) + pair], sn = p.sin_t[(int64_t)pos * (C / 2) + pair];
-            const float a = x[e], bb = x[e + 1];
-            x[e] = __fsub_rn(__fmul_rn(cs, a), __fmul_rn(sn, bb));
-            x[e + 1] = __fadd_rn(__fmul_rn(sn, a), __fmul_rn(cs, bb));
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) raw[e] = __float2bfloat16_rn(x[e]);
       }
-      if (EPL == 4) {
-        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(raw);
-      } else {
-        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(raw);
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int64_t row = row0 + r * warps;
+      if (row >= rows) continue;  // warp-uniform
+      const int h = hh[r], l = ll[r], b = bb_[r];
+#pragma unroll
+      for (int which = 0; which < 3; ++which) {
+        __nv_bfloat16 el[EPL];
+        *reinterpret_cast<Vec*>(el) = raw[r][which];
+        __nv_bfloat16* dst;
+        if (which == 0) {
+          dst = p.q_out + b * p.q_sb + h * p.q_sh + (int64_t)l * p.q_sl;
+        } else if (which == 1) {
+          dst = p.k_cache + b * p.k_sb + h * p.k_sh + (int64_t)(p.cache_pos + l) * p.k_sl;
+        } else {
+          dst = p.v_cache + b * p.v_sb + h * p.v_sh + (int64_t)(p.cache_pos + l) * p.v_sl;
+        }
+        dst += lane * EPL;
+        if (which < 2) {
+          float x[EPL];
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(el[e]);
+          if (p.scale_mul != nullptr) {
+            float ssq = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) ssq = fmaf(x[e], x[e], ssq);
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, d);
+            const float denom = fmaxf(sqrtf(ssq), 1e-12f);
+            const float mul = which == 0 ? p.scale_mul[h] : 1.0f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+              x[e] = __fdiv_rn(x[e], denom);
+              if (which == 0) x[e] = __fmul_rn(x[e], mul);
+            }
+          }
+          if (p.cos_t != nullptr) {
+#pragma unroll
+            for (int e = 0; e < EPL; e += 2) {
+              const float c1 = cs[r][e >> 1], s1 = sn[r][e >> 1];
+              const float a = x[e], b2 = x[e + 1];
+              x[e] = __fsub_rn(__fmul_rn(c1, a), __fmul_rn(s1, b2));
+              x[e + 1] = __fadd_rn(__fmul_rn(s1, a), __fmul_rn(c1, b2));
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) el[e] = __float2bfloat16_rn(x[e]);
+        }
+        *reinterpret_cast<Vec*>(dst) = *reinterpret_cast<const Vec*>(el);
       }
     }
   }
