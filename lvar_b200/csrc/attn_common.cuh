@@ -70,28 +70,6 @@ __device__ __forceinline__ float chunk_max(const uint32_t (&r)[32]) {
   return fmax3(m0, m1, fmaxf(__uint_as_float(r[30]), __uint_as_float(r[31])));
 }
 
-// p = exp2(s * scale - m) for one 32-column chunk: packed FMA, row-sum accumulation in two packed
-// accumulators, bf16x2 packing of the 32 probabilities into pk[off .. off+15].
-__device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], uint64_t sc2, uint64_t nm2, uint64_t& sum_a,
-                                               uint64_t& sum_b, uint32_t (&pk)[32], int off) {
-#pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
-    const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), sc2, nm2);
-    float a0, a1, b0, b1;
-    unpack_f32x2(t0, a0, a1);
-    unpack_f32x2(t1, b0, b1);
-    a0 = fast_exp2(a0);
-    a1 = fast_exp2(a1);
-    b0 = fast_exp2(b0);
-    b1 = fast_exp2(b1);
-    sum_a = fadd2(sum_a, pack_f32x2(a0, a1));
-    sum_b = fadd2(sum_b, pack_f32x2(b0, b1));
-    pk[off + i / 2] = pack_bf16x2(a0, a1);
-    pk[off + i / 2 + 1] = pack_bf16x2(b0, b1);
-  }
-}
-
 // exp2 of two values on the FMA pipe (no MUFU): x = j + f with j = round(x), |f| <= 0.5; 2^f by a
 // degree-4 minimax polynomial (relative error 2.7e-6), 2^j by adding j to the exponent field.
 // Valid for -126 <= x <= 100; the caller guarantees the range (no masked, i.e. -inf, inputs).
@@ -111,6 +89,36 @@ __device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& o0, float& o1) 
   unpack_f32x2(t2, t0, t1);
   o0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
   o1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+// p = exp2(s * scale - m) for one 32-column chunk: packed FMA, row-sum accumulation in two packed
+// accumulators, bf16x2 packing of the 32 probabilities into pk[off .. off+15].
+// Groups of four whose bit is set in POLY take their exponentials from exp2_poly_x2 (inputs clamped at -126,
+// so the caller must not pass masked, i.e. -inf, scores with POLY != 0: they would come out as 2^-126, not 0).
+template <uint32_t POLY = 0>
+__device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], uint64_t sc2, uint64_t nm2, uint64_t& sum_a,
+                                               uint64_t& sum_b, uint32_t (&pk)[32], int off) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const uint64_t t0 = ffma2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
+    const uint64_t t1 = ffma2(pack_f32x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), sc2, nm2);
+    float a0, a1, b0, b1;
+    unpack_f32x2(t0, a0, a1);
+    unpack_f32x2(t1, b0, b1);
+    if ((POLY >> (i / 4)) & 1u) {
+      exp2_poly_x2(pack_f32x2(fmaxf(a0, -126.f), fmaxf(a1, -126.f)), a0, a1);
+      exp2_poly_x2(pack_f32x2(fmaxf(b0, -126.f), fmaxf(b1, -126.f)), b0, b1);
+    } else {
+      a0 = fast_exp2(a0);
+      a1 = fast_exp2(a1);
+      b0 = fast_exp2(b0);
+      b1 = fast_exp2(b1);
+    }
+    sum_a = fadd2(sum_a, pack_f32x2(a0, a1));
+    sum_b = fadd2(sum_b, pack_f32x2(b0, b1));
+    pk[off + i / 2] = pack_bf16x2(a0, a1);
+    pk[off + i / 2 + 1] = pack_bf16x2(b0, b1);
+  }
 }
 
 // exp_pack_chunk without the packing: only the row sum of the 32 exponentials is kept.
