@@ -263,6 +263,32 @@ def timed(fn, iters, warm=3):
     return a.elapsed_time(b) / iters
 
 
+def timed_interleaved(fns, iters=4, rounds=7, warm=2, spread=False):
+    """Median milliseconds per call of each function in `fns`, the functions taking turns in blocks of `iters`
+    calls for `rounds` rounds: ratios between them are then taken at the same clocks and temperature.  With
+    `spread`, (median, fastest round, slowest round) per function."""
+    for fn in fns:
+        for _ in range(warm):
+            fn()
+    torch.cuda.synchronize()
+    marks = []
+    for _ in range(rounds):
+        for i, fn in enumerate(fns):
+            a, b = ev(), ev()
+            fn()  # untimed: the timed calls of this block start on a busy GPU
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            marks.append((i, a, b))
+    torch.cuda.synchronize()
+    out = []
+    for i in range(len(fns)):
+        ms = sorted(a.elapsed_time(b) / iters for j, a, b in marks if j == i)
+        out.append(statistics.median(ms) if not spread else (statistics.median(ms), ms[0], ms[-1]))
+    return out
+
+
 def max_over_ranks(x: float, dev, world: int) -> float:
     if world == 1:
         return x
@@ -521,9 +547,13 @@ def run_ours(args):
     dense_flops = 4.0 * B * H * LQ * LKV * D
     extra = {}
     if not args.no_extra:
-        dense_ms = timed(lambda: K.dense_attn_fwd(q, k, v, scale), 10)
+        # dense attention, attention + column sums in one launch (two sweeps), and the one-sweep form on given
+        # statistics take turns, so that the overheads below are ratios at the same clocks
+        (dense_ms, d_lo, d_hi), (fused_ms, f_lo, f_hi), (given_ms, g_lo, g_hi) = timed_interleaved([
+            lambda: K.dense_attn_fwd(q, k, v, scale),
+            lambda: K.dense_colsum_attn_fwd(q, k, v, scale),
+            lambda: K.dense_colsum_attn_given_fwd(q, k, v, M, L, scale)], iters=6, rounds=9, spread=True)
         colsum_ms = timed(lambda: K.colsum_fwd(q, k, M, L, BLOCK, scale), 10)
-        fused_ms = timed(lambda: K.dense_colsum_attn_fwd(q, k, v, scale), 10)  # attention + column sums, one launch
         cs_only_ms = timed(lambda: K.colsum_tiles_fwd(q, k, scale), 10)
         cs_given_ms = timed(lambda: K.colsum_tiles_fwd(q, k, scale, stats=(M, L)), 10)
         mask_ms = timed(lambda: K.block_mask_from_colsums(cs, always, K_TOTAL, BLOCK), 10)
@@ -535,22 +565,26 @@ def run_ours(args):
             "colsum_over_dense_attn": (fused_ms - dense_ms) / dense_ms,
             "colsum_over_dense_attn_separate_kernels": colsum_ms / dense_ms,
             "mask_build_us": mask_ms * 1e3, "density": K_TOTAL / nk})
-        if hasattr(K, "dense_colsum_attn_given_fwd"):
-            # the form the reference's CUDA operator has: row statistics supplied, ONE sweep, column sums of the
-            # same probabilities that feed P V
-            given_ms = timed(lambda: K.dense_colsum_attn_given_fwd(q, k, v, M, L, scale), 10)
-            extra["dense_colsum_stats_given_ms"] = given_ms
-            extra["colsum_over_dense_attn_stats_given"] = (given_ms - dense_ms) / dense_ms
+        # the form the reference's CUDA operator has: row statistics supplied, ONE sweep, column sums of the same
+        # probabilities that feed P V
+        extra["dense_colsum_stats_given_ms"] = given_ms
+        extra["colsum_over_dense_attn_stats_given"] = (given_ms - dense_ms) / dense_ms
+        # fastest and slowest of the nine interleaved rounds of each kernel (the one-sweep kernel's time moves by
+        # several per cent with the clocks the power cap allows at that moment)
+        extra["colsum_timing_spread_ms"] = {"dense_attn": [round(d_lo, 4), round(d_hi, 4)],
+                                            "dense_colsum_fused": [round(f_lo, 4), round(f_hi, 4)],
+                                            "dense_colsum_stats_given": [round(g_lo, 4), round(g_hi, 4)]}
 
         # ---- scheduling A/B on the headline kernel and on dense attention (same launch, different hand-out of
         # the last wave): pairs only / single tiles on one half of the CTA / single tiles split over both halves
-        ab = {}
-        for tag, flags in (("pairs_only", _lib.SCHED_PAIRS_ONLY), ("single_tiles_one_half", _lib.SCHED_SINGLE_ONE_SLOT),
-                           ("single_tiles_split", 0)):
-            ms_b = timed(lambda: K.block_sparse_attn_fwd(q, k, v, mask, scale, sched_flags=flags), 20, warm=5)
-            ms_d = timed(lambda: K.dense_attn_fwd(q, k, v, scale, sched_flags=flags), 10)
-            ab[tag] = {"block_sparse_tflops": round(flops / ms_b / 1e9, 1), "dense_tflops": round(dense_flops / ms_d / 1e9, 1)}
-        extra["schedule_ab"] = ab
+        tags = (("pairs_only", _lib.SCHED_PAIRS_ONLY), ("single_tiles_one_half", _lib.SCHED_SINGLE_ONE_SLOT),
+                ("single_tiles_split", 0))
+        ms_b = timed_interleaved([(lambda f=f: K.block_sparse_attn_fwd(q, k, v, mask, scale, sched_flags=f))
+                                  for _, f in tags], iters=10)
+        ms_d = timed_interleaved([(lambda f=f: K.dense_attn_fwd(q, k, v, scale, sched_flags=f)) for _, f in tags])
+        extra["schedule_ab"] = {tag: {"block_sparse_tflops": round(flops / ms_b[i] / 1e9, 1),
+                                      "dense_tflops": round(dense_flops / ms_d[i] / 1e9, 1)}
+                                for i, (tag, _) in enumerate(tags)}
 
         # ---- the column-sparse kernel on a list shaped like a last-scale sparse step: per 256-row query group
         # 1664 scattered keys (the decision scale's top-k) followed by a band of 512 consecutive keys
