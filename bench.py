@@ -58,8 +58,8 @@ WORKLOAD = ("infinity2b-1024px-last-scale block-sparse attention: B2 H16 D128 Lq
             "128x128 blocks, 17/83 active per row (sink<=16x16 + local + top-k by colsum)")
 PRE_ROLL = 8  # untimed steps queued between the synchronize and the start event of the timed region
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel<128, block-sparse> launch on this
-# workload (one ncu capture of the full launch): 166.5 MB read + 20.0 MB written
-TRAFFIC_BYTES_PER_LAUNCH = 186.5e6
+# workload (one ncu capture of two full launches): 167.9 / 167.2 MB read + 27.0 / 21.8 MB written
+TRAFFIC_BYTES_PER_LAUNCH = 192.0e6
 C5_PROMPTS = 16       # prompts per generated batch of the full-loop configuration (x2 for guidance)
 
 
