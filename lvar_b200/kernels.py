@@ -82,11 +82,27 @@ def read_status(status: torch.Tensor) -> Tuple[int, str]:
     return code, _lib.DEV_STATUS_NAMES.get(code, f"unknown status {code}")
 
 
-def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None, sched_flags=0):
-    """o = softmax(q k^T * scale) v; returns (o, M, L) with fp32 [B,H,Lq] statistics in base 2."""
+def _output_like(q: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+    """The output tensor of an attention call: a fresh contiguous one, or the caller's ``out`` (bf16, q's shape
+    and device, unit stride along the head dimension, every other stride a multiple of 8 elements and a 16-byte
+    aligned base, e.g. a [B,H,L,D] view of a [B,L,H,D] buffer)."""
+    if out is None:
+        return torch.empty_like(q, memory_format=torch.contiguous_format)
+    if out.dtype != torch.bfloat16 or out.device != q.device or out.shape != q.shape:
+        raise RuntimeError(f"out must be a bfloat16 tensor of shape {tuple(q.shape)} on {q.device}")
+    if out.stride(-1) != 1 or any(st % 8 for st in out.stride()[:-1]) or out.data_ptr() % 16:
+        raise RuntimeError("out needs unit stride along the head dimension, other strides in multiples of 8 "
+                           "elements and a 16-byte aligned base")
+    return out
+
+
+def dense_attn_fwd(q, k, v, scale=None, *, return_stats=True, status=None, wait_limit_ns=None, sched_flags=0,
+                   out=None):
+    """o = softmax(q k^T * scale) v; returns (o, M, L) with fp32 [B,H,Lq] statistics in base 2.  ``out``: an
+    optional destination for o (see :func:`_output_like`)."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
-    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    o = _output_like(q, out)
     B, H, Lq, _ = q.shape
     M = L = None
     a = AttnArgs()
@@ -253,9 +269,10 @@ def heaviest_first_order(block_mask: torch.Tensor, B: int, H: int, block: int = 
 
 
 def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False, status=None, block=128,
-                          work_order=None, sched_flags=0):
+                          work_order=None, sched_flags=0, out=None):
     """Attention under a block mask of 128x128 (or 64x64) blocks: uint8/bool [nq,nk], [H,nq,nk] or [B,H,nq,nk].
-    ``work_order``: optional int32 permutation of the work items (see :func:`heaviest_first_order`)."""
+    ``work_order``: optional int32 permutation of the work items (see :func:`heaviest_first_order`).
+    ``out``: an optional destination for o (see :func:`_output_like`)."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(n, t)
     B, H, Lq, _ = q.shape
@@ -275,7 +292,7 @@ def block_sparse_attn_fwd(q, k, v, block_mask, scale=None, *, return_stats=False
                            f"[{B}|1, {H}|1, {nq}, {nk}]")
     if m.stride(-1) != 1:
         m = m.contiguous()
-    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    o = _output_like(q, out)
     a = AttnArgs()
     stream = _fill_qkv(a, q, k, v, o, scale)
     a.block_mask = m.data_ptr()

@@ -632,3 +632,83 @@ def test_csp_attn_many_work_items_per_sm(K, bm, resize):
         assert d.max().item() <= 3.2e-2 and d.mean().item() <= O_MEAN, (b, h, d.max().item())
     assert torch.equal(o, K.csp_attn_fwd(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), counts.cuda(), o_in.cuda(), 1, bm,
                                          resize_from=resize)), "bit-reproducible"
+
+
+def test_output_into_a_strided_destination_matches_the_default_one(K):
+    """`out=`: o written into a [B,H,L,D] view of a [B,L,H,D] buffer (the layout the next projection reads), and
+    into a view whose rows start on 16-byte but not on 32-byte boundaries (the epilogue then falls back from
+    256-bit to 128-bit stores); both bit-identical to the default contiguous output, for the block-sparse and the
+    dense kernel, ragged last tiles included."""
+    B, H, Lq, Lkv, D = 2, 3, 700, 1300, 128
+    q, k, v = (t.cuda() for t in _qkv(B, H, Lq, Lkv, D, seed=77))
+    nq, nk = (Lq + 127) // 128, (Lkv + 127) // 128
+    g = torch.Generator().manual_seed(5)
+    mask = (torch.rand(B, H, nq, nk, generator=g) < 0.4)
+    mask[..., 0] = True
+    mask = mask.cuda()
+    ref_b = K.block_sparse_attn_fwd(q, k, v, mask)
+    ref_d, _, _ = K.dense_attn_fwd(q, k, v)
+    # (1) [B,L,H,D] buffer, 32-byte aligned rows
+    buf = torch.full((B, Lq, H, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = buf.permute(0, 2, 1, 3)
+    assert K.block_sparse_attn_fwd(q, k, v, mask, out=out) is out
+    assert torch.equal(out, ref_b)
+    # (2) rows of D + 8 elements, first row 16 bytes into the buffer: 16-byte aligned only
+    wide = torch.full((B, H, Lq, D + 8), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out2 = wide[..., 8:]
+    assert out2.data_ptr() % 32 == 16
+    K.block_sparse_attn_fwd(q, k, v, mask, out=out2)
+    assert torch.equal(out2, ref_b)
+    assert torch.isnan(wide[..., :8].float()).all(), "nothing outside the destination is written"
+    wide.fill_(float("nan"))
+    K.dense_attn_fwd(q, k, v, out=out2)
+    assert torch.equal(out2, ref_d)
+    with pytest.raises(RuntimeError):
+        K.dense_attn_fwd(q, k, v, out=wide[..., 4:4 + D])  # base 8 bytes off
+
+
+def test_seeded_sweep_of_ragged_shapes_against_the_oracle(K):
+    """Twenty-four seeded random problems (ragged query and key lengths from 1 to ~900, both head dimensions, both
+    mask block widths, masks with empty block rows, dense / block-sparse / fused column sums on the same tensors):
+    every output within the output bar of the fp64 oracle (relative to max(1, |o|)), column sums within 1e-3
+    element-wise."""
+    from oracle import attention as oa
+    rng = torch.Generator().manual_seed(20240607)
+
+    def _check_o(o_gpu, o_ref):
+        # rows that attend a handful of keys have outputs of magnitude 2 to 4, where one bf16 ulp (1.6e-2 to
+        # 3.1e-2) is itself of the size of the absolute bar: the error is taken relative to max(1, |o|)
+        d = (o_gpu.float().cpu() - o_ref.float()).abs() / o_ref.float().abs().clamp_min(1.0)
+        assert torch.isfinite(o_gpu.float()).all()
+        assert d.max().item() <= O_MAX and d.mean().item() <= O_MEAN, (d.max().item(), d.mean().item())
+
+    def ri(lo, hi):
+        return int(torch.randint(lo, hi + 1, (1,), generator=rng))
+
+    for case in range(24):
+        B, H, D = ri(1, 2), ri(1, 3), (64, 128)[case % 2]
+        Lq, Lkv = ri(1, 900), ri(1, 900)
+        if case % 6 == 0:
+            Lq = ri(1, 3) * 128  # whole tiles
+        if case % 8 == 1:
+            Lkv = ri(1, 40)      # far less than one tile of keys
+        q, k, v = _qkv(B, H, Lq, Lkv, D, seed=1000 + case, peaked=bool(case % 3 == 0))
+        qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+        st = K.new_status("cuda")
+        o, M, L = K.dense_attn_fwd(qc, kc, vc, status=st)
+        _ok_status(K, st)
+        o_ref, cs_ref = oa.dense_colsum_attn(q, k, v, D ** -0.5, q_group_size=128, dtype=torch.float64)
+        _check_o(o, o_ref)
+        o2, cs = K.dense_colsum_attn_fwd(qc, kc, vc, status=st)
+        _ok_status(K, st)
+        _check_o(o2, o_ref)
+        assert _cs_rel(cs, cs_ref) <= CS_REL, f"case {case}: column sums {tuple(q.shape)} x {Lkv}"
+        block = (128, 64)[(case // 2) % 2]
+        nq, nk = (Lq + block - 1) // block, (Lkv + block - 1) // block
+        bm = torch.rand(B, H, nq, nk, generator=rng) < 0.5
+        bm[..., 0] = True
+        if nq > 1:
+            bm[0, 0, nq - 1] = False  # an empty block row: zeros
+        ob = K.block_sparse_attn_fwd(qc, kc, vc, bm.cuda(), block=block, status=st)
+        _ok_status(K, st)
+        _check_o(ob, oa.block_sparse_attn(q, k, v, bm, block=block))
