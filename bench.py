@@ -741,7 +741,7 @@ def run_ours(args):
             del q, k, v
             torch.cuda.empty_cache()
             try:
-                extra["c5_generation_loop"] = leg_c5(dev, world, rank, ("sparse", "dense"), iters=2)
+                extra["c5_generation_loop"] = leg_c5(dev, world, rank, ("sparse", "dense", "none"), iters=2)
             except Exception as e:
                 extra["c5_generation_loop"] = {"failed": f"{type(e).__name__}: {str(e)[:300]}"}
 
