@@ -43,7 +43,8 @@ typedef struct lvar_attn_args {
   /* problem */
   int32_t B, H, Lq, Lkv, D; /* D in {64, 128}; query heads == kv heads */
   float scale;              /* softmax scale (> 0), applied to q.k before the softmax */
-  /* q [B,H,Lq,D], k/v [B,H,Lkv,D], o [B,H,Lq,D]: bf16, 16-byte aligned, strides multiples of 8 */
+  /* q [B,H,Lq,D], k/v [B,H,Lkv,D], o [B,H,Lq,D]: bf16, 16-byte aligned, strides multiples of 8
+     (an o whose base and strides are multiples of 32 bytes is written with 256-bit stores) */
   const void* q;
   int64_t q_sb, q_sh, q_sl;
   const void* k;

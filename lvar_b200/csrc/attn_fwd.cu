@@ -7,8 +7,8 @@
 // same round is loaded once (always the case for dense and column-sparse attention).
 //   warps 0-3   softmax warpgroup of slot 0 (thread = one query row = one TMEM lane)
 //   warps 4-7   softmax warpgroup of slot 1
-//   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp (each lane
-//               copies four whole rows; the tile's barrier takes one arrival per lane as its copies land)
+//   warp  8     K loader (+ the two Q tiles): TMA, or 16-byte cp.async row gathers for csp (four lanes share
+//               a row; the tile's barrier takes one arrival per lane as its copies land)
 //   warp  9     V loader
 //   warp  10    allocates TMEM; lane 0 issues every tcgen05.mma (descriptor words precomputed, all lanes
 //               run the bookkeeping so that it stays out of a divergent branch)
@@ -38,7 +38,7 @@ namespace lvar {
 
 namespace {
 
-constexpr int kThreads = 384;  // 8 softmax warps + K loader + V loader + MMA issuer + 1 idle warp
+constexpr int kThreads = 384;  // 8 softmax warps + K loader + V loader + MMA issuer + scheduler
 constexpr int kRegsSoftmax = 208, kRegsOther = 72;
 constexpr int kMaxSteps = 1024;  // per-slot KV tile list capacity (block-sparse: Lkv <= 131072)
 constexpr int kStages = 2;
