@@ -110,6 +110,7 @@ typedef struct lvar_attn_args {
 
 #define LVAR_SCHED_PAIRS_ONLY 1     /* never hand the last wave out as single tiles */
 #define LVAR_SCHED_SINGLE_ONE_SLOT 2 /* a single tile runs on one half of the CTA (no KV split, no merge) */
+#define LVAR_SCHED_SERIALIZE_LAUNCH 4 /* launch without the programmatic-dependent-launch attribute */
 
 /* Dense attention o = softmax(q k^T * scale) v with row statistics.
  * Replaces torch.ops.chipmunk.dense_attn (kernels/chipmunk/csrc/attn/dense_attn.cu:248-372) and

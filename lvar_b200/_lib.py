@@ -22,7 +22,7 @@ DEV_STATUS_NAMES = {
     6: "forced timeout (wait limit 0)",
 }
 DEFAULT_WAIT_NS = 2_000_000_000
-SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT = 1, 2  # lvar_attn_args.sched_flags
+SCHED_PAIRS_ONLY, SCHED_SINGLE_ONE_SLOT, SCHED_SERIALIZE_LAUNCH = 1, 2, 4  # lvar_attn_args.sched_flags
 
 
 class LvarError(RuntimeError):

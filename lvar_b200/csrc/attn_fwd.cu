@@ -243,6 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_relinquish();
   }
   if (warp == 8 && lane == 0) {
+    griddep_launch_dependents();  // the next grid in the stream may take an SM as soon as this CTA has left it
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -1183,6 +1184,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // Hands out work items from a global counter and builds each item's KV-tile list, one item ahead
     // of the slowest role.  The counter pair resets itself when the last CTA leaves.
     setmaxnreg_dec<kRegsOther>();
+    // Everything before this point (barriers, TMEM, descriptors) touched no global memory and may have run
+    // under the tail of the grid before this one in the stream; the work counter, the inputs and the output
+    // are only touched after that grid has completed.  Every other role starts from an item this warp publishes.
+    griddep_wait();
     bool ok = true;
     for (int n = 0; ok; ++n) {
       const int slot = n % kSchedStages;
@@ -1316,7 +1321,7 @@ namespace {
 
 template <int D, int MODE>
 int launch_mode(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, dim3 grid,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool serialize_launch) {
   auto kern = attn_fwd_kernel<D, MODE>;
   static bool attr_set[16] = {false};
   int dev = 0;
@@ -1327,21 +1332,31 @@ int launch_mode(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   } else if (dev >= 16) {
     LVAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kDynamic));
   }
-  kern<<<grid, kThreads, Smem<D>::kDynamic, stream>>>(tq, tk, tv, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Smem<D>::kDynamic;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = serialize_launch ? 0 : 1;
+  LVAR_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, p));
   LVAR_CUDA_OK(cudaGetLastError());
   return LVAR_OK;
 }
 
 template <int D>
 int launch_d(int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
-             dim3 grid, cudaStream_t stream) {
+             dim3 grid, cudaStream_t stream, bool serialize_launch) {
   switch (mode) {
-    case MODE_DENSE: return launch_mode<D, MODE_DENSE>(tq, tk, tv, p, grid, stream);
-    case MODE_BLOCK: return launch_mode<D, MODE_BLOCK>(tq, tk, tv, p, grid, stream);
-    case MODE_DENSE_CS: return launch_mode<D, MODE_DENSE_CS>(tq, tk, tv, p, grid, stream);
-    case MODE_CS_ONLY: return launch_mode<D, MODE_CS_ONLY>(tq, tk, tv, p, grid, stream);
-    case MODE_DENSE_CS1: return launch_mode<D, MODE_DENSE_CS1>(tq, tk, tv, p, grid, stream);
-    default: return launch_mode<D, MODE_CSP>(tq, tk, tv, p, grid, stream);
+    case MODE_DENSE: return launch_mode<D, MODE_DENSE>(tq, tk, tv, p, grid, stream, serialize_launch);
+    case MODE_BLOCK: return launch_mode<D, MODE_BLOCK>(tq, tk, tv, p, grid, stream, serialize_launch);
+    case MODE_DENSE_CS: return launch_mode<D, MODE_DENSE_CS>(tq, tk, tv, p, grid, stream, serialize_launch);
+    case MODE_CS_ONLY: return launch_mode<D, MODE_CS_ONLY>(tq, tk, tv, p, grid, stream, serialize_launch);
+    case MODE_DENSE_CS1: return launch_mode<D, MODE_DENSE_CS1>(tq, tk, tv, p, grid, stream, serialize_launch);
+    default: return launch_mode<D, MODE_CSP>(tq, tk, tv, p, grid, stream, serialize_launch);
   }
 }
 
@@ -1510,8 +1525,9 @@ int launch_attention(const lvar_attn_args* a, int mode, cudaStream_t stream) {
     if (rc != LVAR_OK) return rc;
   }
 
-  if (a->D == 128) return launch_d<128>(mode, tq, tk, tv, p, grid, stream);
-  return launch_d<64>(mode, tq, tk, tv, p, grid, stream);
+  const bool serialize_launch = (a->sched_flags & LVAR_SCHED_SERIALIZE_LAUNCH) != 0;
+  if (a->D == 128) return launch_d<128>(mode, tq, tk, tv, p, grid, stream, serialize_launch);
+  return launch_d<64>(mode, tq, tk, tv, p, grid, stream, serialize_launch);
 }
 
 }  // namespace lvar

@@ -375,6 +375,12 @@ template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+// Programmatic dependent launch: a grid launched with the programmatic-stream-serialization attribute may start
+// while the grid before it in the stream is still running.  griddep_wait blocks until that grid has completed and
+// its writes are visible (a no-op for a normal launch); griddep_launch_dependents lets the next grid's CTAs be
+// scheduled as soon as resources free up.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // 256-bit global store (sm_100): p must be 32-byte aligned.
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
