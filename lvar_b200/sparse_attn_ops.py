@@ -145,15 +145,29 @@ def topk_indices(activations: torch.Tensor, indices_out: torch.Tensor, counts_ou
     ``counts_out[b, r]`` with count (sparse_attn_ops.py:381-389).  The reference kernel keeps roughly
     the top (1 - sparsity_amount) fraction through a sampled quantile, in a run-dependent order; this
     one keeps exactly ceil((1 - sparsity_amount) * cols) columns rounded up to ``multiple_of``, in
-    descending order of value (lower index first among equals).  ``rk`` (random extra keys) must be 0."""
+    descending order of value (lower index first among equals).
+
+    ``rk`` > 0 (the reference's ``random_amount``, kernels/chipmunk/csrc/indexed_io/topk_indices.cu:108): every
+    column outside the exact selection joins it with probability ``rk``, drawn from torch's CUDA generator (so
+    ``torch.manual_seed`` makes it repeatable, which the reference's per-thread curand streams seeded from the
+    data are not); the count is then padded to ``multiple_of`` with unselected columns, and the order within a
+    row is that of ``mask_to_indices`` (the reference's is the order of its atomics)."""
     assert activations.dim() == 3, "activation must be 3-dimensional [batch, rows, cols]"
     assert indices_out.dim() == 3, "indices must be 3-dimensional [batch, rows, cols]"
     assert counts_out.dim() == 2, "counts must be 2-dimensional [batch, rows]"
     assert 0 <= sparsity_amount <= 1, "sparsity_amount must be between 0 and 1"
-    if rk != 0:
-        raise NotImplementedError("random keys are not supported: the selection is deterministic")
+    assert 0 <= rk <= 1, "rk (random amount) must be between 0 and 1"
     cols = activations.shape[-1]
     keep = min(cols, math.ceil((1.0 - sparsity_amount) * cols))
+    if rk > 0 and 0 < keep < cols:
+        exact = K.topk_indices(activations.float(), keep)
+        mask = torch.zeros(activations.shape, dtype=torch.bool, device=activations.device)
+        mask.scatter_(-1, exact.long(), True)
+        mask |= torch.rand(activations.shape, device=activations.device) < rk
+        inds, counts = K.mask_to_indices(mask.unsqueeze(0), multiple_of, 1)
+        indices_out[..., :cols].copy_(inds[0][..., :cols])
+        counts_out.copy_(counts[0].clamp_max(cols))
+        return
     keep = min(cols, (keep + multiple_of - 1) // multiple_of * multiple_of) if keep > 0 else 0
     inds, counts = K.topk_indices(activations.float(), keep, out_cols=indices_out.shape[-1], with_counts=True)
     indices_out.copy_(inds)

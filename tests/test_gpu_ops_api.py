@@ -87,8 +87,29 @@ def test_index_ops_signatures(ops):
     assert (counts == 1000).all()
     ops.topk_indices(act.cuda(), inds, counts, 1.0, 64, 0.0)
     assert (counts == 0).all()
-    with pytest.raises(NotImplementedError):
-        ops.topk_indices(act.cuda(), inds, counts, 0.5, 64, 0.1)
+    # random extra keys: the exact top half is always inside, about rk of the rest joins, counts are padded to a
+    # multiple of 64, and the draw repeats under the same seed
+    inds.fill_(-1)
+    torch.manual_seed(11)
+    ops.topk_indices(act.cuda(), inds, counts, 0.5, 64, 0.1)
+    first = (inds.clone(), counts.clone())
+    assert (counts % 64 == 0).all() or (counts == 1000).all()
+    exact = oi.topk_indices(act, 500)
+    n_extra = 0
+    for b in range(2):
+        for r in range(5):
+            c = int(counts[b, r])
+            got = set(inds[b, r, :c].cpu().tolist())
+            assert len(got) == c and set(exact[b, r].tolist()) <= got and max(got) < 1000 and min(got) >= 0
+            n_extra += c - 500
+    assert 10 * (0.1 * 500 - 35) <= n_extra <= 10 * (0.1 * 500 + 35 + 63)  # binomial(500, 0.1) per row, + padding
+    torch.manual_seed(11)
+    ops.topk_indices(act.cuda(), inds, counts, 0.5, 64, 0.1)
+    assert torch.equal(counts, first[1])
+    for b in range(2):
+        for r in range(5):
+            c = int(counts[b, r])
+            assert torch.equal(inds[b, r, :c], first[0][b, r, :c])
     with pytest.raises(NotImplementedError):
         ops.copy_indices(None, None, None, None)
     packed, shp = ops.bitpack(m.cuda())
