@@ -712,3 +712,35 @@ def test_seeded_sweep_of_ragged_shapes_against_the_oracle(K):
         ob = K.block_sparse_attn_fwd(qc, kc, vc, bm.cuda(), block=block, status=st)
         _ok_status(K, st)
         _check_o(ob, oa.block_sparse_attn(q, k, v, bm, block=block))
+
+
+def test_overlapped_launches_keep_stream_order_for_data(K):
+    """Attention launches may begin their set-up under the tail of the kernel before them (programmatic dependent
+    launch).  A chain in which every launch consumes the output of the one before it, queued without any host
+    synchronisation, gives the same bits as the same chain with plain launches, and a launch that follows a torch
+    kernel writing its input sees that kernel's result."""
+    from lvar_b200 import _lib
+    B, H, L, D = 2, 4, 600, 128
+    q, k, v = (t.cuda() for t in _qkv(B, H, L, L, D, seed=31))
+
+    def chain(flags):
+        x = q.clone()
+        for _ in range(12):
+            x, _, _ = K.dense_attn_fwd(x, k, v, sched_flags=flags)
+            x = x * 2.0  # a torch kernel between two launches: writes the next launch's input
+        torch.cuda.synchronize()
+        return x
+
+    a = chain(_lib.SCHED_SERIALIZE_LAUNCH)
+    for _ in range(3):
+        assert torch.equal(chain(0), a)
+    # back-to-back launches of ours with nothing in between, each reading the previous one's output
+    def chain2(flags):
+        x = q.clone()
+        outs = []
+        for _ in range(12):
+            x = K.block_sparse_attn_fwd(x, k, v, torch.ones(5, 5, dtype=torch.bool, device="cuda"), sched_flags=flags)
+            outs.append(x)
+        torch.cuda.synchronize()
+        return outs[-1]
+    assert torch.equal(chain2(0), chain2(_lib.SCHED_SERIALIZE_LAUNCH))
