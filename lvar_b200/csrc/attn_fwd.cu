@@ -591,6 +591,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // ---- epilogue: O / l -> bf16 -> global; row statistics
       const bool split = (MODE == MODE_DENSE || MODE == MODE_BLOCK) && im.split;
       float m_stat = m_true, l_stat = (it > 0 && l > 0.f) ? l * fast_exp2(m_ref - m_true) : 0.f;
+      if (MODE == MODE_CSP && row_ok) {
+        // Column-sparse: the epilogue adds this row of the accumulate input (or the four rows of the coarser grid
+        // it is resized from).  Its 16-byte loads sit between stores they may not pass (o_in may alias o), one
+        // exposed memory latency each; bring the lines close while the last P V is still running.
+        const __nv_bfloat16* ib = p.o_in + im.b * p.oi_sb + im.h * p.oi_sh;
+        if (p.oi_side > 0) {
+          const BilinearTaps tp = bilinear_taps(row / p.o_side, row % p.o_side, p.oi_side, p.oi_ratio);
+          const int rows4[4] = {tp.r00, tp.r01, tp.r10, tp.r11};
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int b128 = 0; b128 < D * 2; b128 += 128)
+              prefetch_l1(reinterpret_cast<const char*>(ib + (int64_t)rows4[t] * p.oi_sl) + b128);
+        } else {
+#pragma unroll
+          for (int b128 = 0; b128 < D * 2; b128 += 128)
+            prefetch_l1(reinterpret_cast<const char*>(ib + (int64_t)row * p.oi_sl) + b128);
+        }
+      }
       if (MODE != MODE_CS_ONLY) {
         if (it > 0) {
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, wc, DEV_TIMEOUT_SOFTMAX));

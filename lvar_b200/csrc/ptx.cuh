@@ -381,6 +381,7 @@ __device__ __forceinline__ void setmaxnreg_dec() {
 // scheduled as soon as resources free up.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 // 256-bit global store (sm_100): p must be 32-byte aligned.
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
