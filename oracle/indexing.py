@@ -265,7 +265,8 @@ def mask_to_indices(mask: torch.Tensor, multiple_of: int, pad_to_multiple_of: in
     of one warp owns columns t, t+32, ... and writes its set columns, ascending, at the exclusive
     prefix of the lanes' counts - so the list is grouped by (column mod 32).  The count is rounded
     up to ``multiple_of`` and the list is padded with the first unset columns.  Entries past the
-    count are undefined in the reference (torch.empty); here they are -1.
+    count are undefined in the reference (torch.empty); here they are -1.  Checked against the reference
+    kernel itself, compiled for sm_100a by ``oracle/build_ref.py``, in tests/test_gpu_reference_kernels.py.
     """
     b, h, m, n = mask.shape
     pad_n = (n + pad_to_multiple_of - 1) // pad_to_multiple_of * pad_to_multiple_of
