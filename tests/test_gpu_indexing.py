@@ -178,3 +178,24 @@ def test_block_mask_from_colsums_equals_two_kernels(K, B, H, G, Lkv, block, k_to
     assert torch.equal(mask.cpu(), oi.build_block_mask(scores.cpu(), always, k_total))
     assert torch.equal(K.block_mask_from_colsums(csc, None, k_total, block),
                        K.build_block_mask(scores, None, k_total))
+
+
+def test_topk_is_torch_topk_on_the_same_gpu(K):
+    """The decision step of the reference takes ``torch.topk(bs, k, dim=-1).indices`` (models/sparvar/sparse_attn.py:
+    1012-1039).  On scores without ties this package's kernel returns the same index SEQUENCE (descending by value);
+    with ties, where torch.topk's order is not defined, the same multiset of values and the lower-index-first rule."""
+    g = torch.Generator(device="cuda").manual_seed(17)
+    for rows, n, k in ((64, 4121, 824), (32, 10521, 2176), (7, 257, 257), (5, 1000, 1)):
+        s = torch.rand(rows, n, generator=g, device="cuda").argsort(-1).float() * 0.37 - 100.0  # distinct values
+        got = K.topk_indices(s, k)
+        ref = torch.topk(s, k, dim=-1).indices
+        assert torch.equal(got.long(), ref)
+    # ties: quantised scores
+    s = (torch.randn(16, 4121, generator=g, device="cuda") * 4).round()
+    k = 600
+    got = K.topk_indices(s, k).long()
+    ref = torch.topk(s, k, dim=-1)
+    assert torch.equal(torch.gather(s, -1, got), ref.values)          # the same values, in descending order
+    same_val = torch.gather(s, -1, got)
+    inc = (got[:, 1:] > got[:, :-1]) | (same_val[:, 1:] != same_val[:, :-1])
+    assert inc.all()                                                   # lower index first among equals
